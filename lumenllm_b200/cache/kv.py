@@ -51,10 +51,20 @@ def _aligned_zeros(shape, dtype, device, align=1024):
 
 @dataclass(frozen=True)
 class CacheNeed:
-    """What a mixer asks of the cache for one entry."""
+    """What a mixer asks of the cache for one entry. `v_dim` is the width of a value where it
+    differs from a key's (0: the same); `keep_first` first tokens of a sequence stay in sight of
+    every later query although a window is set; `layout` fixes the tile layout (None: by type
+    and head size)."""
     n_kv: int
     head_dim: int
     window: int = 0   # 0: all keys
+    v_dim: int = 0
+    keep_first: int = 0
+    layout: Optional[int] = None
+
+    @property
+    def value_dim(self) -> int:
+        return self.v_dim or self.head_dim
 
 
 def pages_for(n_tokens: int) -> int:
@@ -70,22 +80,28 @@ class CacheGroup:
         self.pool = PagePool(n_pages, reserved=1)
         total = n_pages + 1
         shape = (len(self.entries), total, need.n_kv, PAGE, need.head_dim)
-        self.layout = tile_layout(dtype, need.head_dim)
+        vshape = (len(self.entries), total, need.n_kv, PAGE, need.value_dim)
+        self.layout = tile_layout(dtype, need.head_dim) if need.layout is None else need.layout
+        self.v_layout = tile_layout(dtype, need.value_dim) if need.layout is None else need.layout
         if device is not None:
             self.k = _aligned_zeros(shape, dtype, device)
-            self.v = _aligned_zeros(shape, dtype, device)
+            self.v = _aligned_zeros(vshape, dtype, device)
         else:  # bookkeeping only (host tests)
             self.k = self.v = None
         self.table = np.zeros((max_slots, max_pages_per_seq), dtype=np.int32)
-        self.first_page = np.zeros((max_slots,), dtype=np.int64)   # first page index still held
-        self.n_held = np.zeros((max_slots,), dtype=np.int64)       # pages held: [first, first+n)
+        # pages held by a slot: [0, kept) and [first_page, end_page), where kept covers the
+        # first tokens a window keeps in sight (none without such tokens) and never gives back
+        self.keep_pages = pages_for(need.keep_first) if need.window > 0 else 0
+        self.first_page = np.zeros((max_slots,), dtype=np.int64)   # first page of the window's run
+        self.end_page = np.zeros((max_slots,), dtype=np.int64)     # one past the last page held
+        self.n_held = np.zeros((max_slots,), dtype=np.int64)       # pages held in all
 
     def bytes_per_token(self, itemsize: int) -> int:
-        return 2 * len(self.entries) * self.need.n_kv * self.need.head_dim * itemsize
+        return len(self.entries) * self.need.n_kv * (self.need.head_dim + self.need.value_dim) * itemsize
 
     def reserve(self, slot: int, new_len: int) -> None:
         want_end = pages_for(new_len)
-        have_end = int(self.first_page[slot] + self.n_held[slot])
+        have_end = int(self.end_page[slot])
         if want_end > self.table.shape[1]:
             raise CacheFull(f"slot {slot}: {new_len} tokens are beyond the longest sequence "
                             f"the cache was built for ({self.table.shape[1] * PAGE})")
@@ -96,6 +112,7 @@ class CacheGroup:
                 raise CacheFull(f"slot {slot}: the cache is full ({e})") from None
             self.table[slot, have_end:want_end] = got
             self.n_held[slot] += want_end - have_end
+            self.end_page[slot] = want_end
 
     def trim(self, slot: int, length: int) -> None:
         """After a step: a group with a window gives back the pages that no later
@@ -103,21 +120,22 @@ class CacheGroup:
         w = self.need.window
         if w <= 0:
             return
-        first_needed = max(0, length - w + 1) // PAGE
-        first = int(self.first_page[slot])
+        first_needed = min(max(0, length - w + 1) // PAGE, int(self.end_page[slot]))
+        first = max(int(self.first_page[slot]), self.keep_pages)    # pages of kept tokens stay
         if first_needed > first:
-            n = min(first_needed - first, int(self.n_held[slot]))
+            n = first_needed - first
             self.pool.give_back(self.table[slot, first:first + n].tolist())
             self.table[slot, first:first + n] = 0
             self.first_page[slot] = first + n
             self.n_held[slot] -= n
 
     def release(self, slot: int) -> None:
-        first, n = int(self.first_page[slot]), int(self.n_held[slot])
-        if n:
-            self.pool.give_back(self.table[slot, first:first + n].tolist())
+        held = self.table[slot][self.table[slot] != 0]       # page 0 is never handed out
+        if held.size:
+            self.pool.give_back(held.tolist())
         self.table[slot, :] = 0
         self.first_page[slot] = 0
+        self.end_page[slot] = 0
         self.n_held[slot] = 0
 
 
@@ -130,18 +148,21 @@ class StateStore:
     device touches no live sequence's state for them. (The reference keeps such state
     per layer for its recurrent mixers: executor/state.rs:640-648.)"""
 
-    def __init__(self, shapes: Dict[int, Tuple[Tuple[int, ...], torch.dtype]], max_slots: int, device):
+    def __init__(self, shapes, max_slots: int, device):
+        """shapes: {entry: (shape, dtype)} for a mixer's state, or {(entry, name): (shape, dtype)}
+        where an entry has several (a block's own state beside its mixer's)."""
         self.pad_row = max_slots
-        self.tensors: Dict[int, torch.Tensor] = {}
-        for entry, (shape, dtype) in shapes.items():
-            self.tensors[entry] = torch.zeros((max_slots + 1, *shape), dtype=dtype, device=device)
+        self.tensors: Dict[Tuple[int, str], torch.Tensor] = {}
+        for key, (shape, dtype) in shapes.items():
+            key = key if isinstance(key, tuple) else (key, "mixer")
+            self.tensors[key] = torch.zeros((max_slots + 1, *shape), dtype=dtype, device=device)
 
     def zero_slot(self, slot: int) -> None:
         for t in self.tensors.values():
             t[slot].zero_()
 
-    def of(self, entry: int) -> Optional[torch.Tensor]:
-        return self.tensors.get(entry)
+    def of(self, entry: int, name: str = "mixer") -> Optional[torch.Tensor]:
+        return self.tensors.get((entry, name))
 
 
 class KVCache:

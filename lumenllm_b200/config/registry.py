@@ -30,10 +30,12 @@ def known_architectures():
 
 
 def config_class_for(d: dict):
-    """`architectures[]` first, then `model_type`
+    """`architectures[]` first (or the single name under `architecture`), then `model_type`
     (crates/aegisllm-base/src/model/mod.rs:136-153, with exact names instead of
     substring matching)."""
-    archs = d.get("architectures") or []
+    archs = list(d.get("architectures") or [])
+    if isinstance(d.get("architecture"), str):
+        archs.append(d["architecture"])
     for a in archs:
         if a in _BY_ARCH:
             return _BY_ARCH[a]

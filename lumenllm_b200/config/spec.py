@@ -28,12 +28,16 @@ class PartSpec:
 class LayerSpec:
     """A block: how a mixer and a feed-forward are arranged around the residual
     stream (`block`, e.g. "pre_norm"), and the parts themselves. Each layer has
-    its own, so one model can mix kinds."""
+    its own, so one model can mix kinds. `ffn` is None for a layer without a feed-forward
+    (where the block arrangement allows that); `extras` holds further parts that an
+    arrangement puts around its sublayers (a convolution of a sublayer's input, say), by the
+    names the arrangement gives them."""
     block: str
     mixer: PartSpec
-    ffn: PartSpec
+    ffn: Optional[PartSpec]
     norms: Dict[str, PartSpec]
     prefix: str = ""
+    extras: Dict[str, PartSpec] = field(default_factory=dict)
 
 
 @dataclass(frozen=True)

@@ -1,0 +1,295 @@
+// Attention whose softmax weights are mixed ACROSS heads before they meet the values
+// ("talking heads" after the softmax), over the paged cache, with a sliding window that keeps
+// the first tokens of a sequence in sight:
+//
+//   a query at position p sees key j if j <= p and (p - j < size or j < keep);
+//   w_g(j) = softmax_j(scale * q_g . k_kv(g)(j)) over the visible keys, per head g;
+//   m_h(j) = sum_g T[h][g] w_g(j);          out_h = sum_j m_h(j) v_kv(h)(j).
+//
+// The mix needs every head's NORMALISED weights at a (query, key) pair, so the weights cannot
+// stay inside one head's running softmax as in flash attention. The work is cut into three
+// kernels around a float32 scratch matrix W[token][head][column]:
+//   1. scores:  W = scale * q . k                       (per head, keys in parallel)
+//   2. softmax over a token's columns per head, then the mix over heads at every column
+//      (in place: W becomes m)
+//   3. values:  out_h = sum over columns of m_h * v     (per head, keys in parallel)
+// Column c of a token stands for key c if c < kept, else key lo + (c - kept), with
+// lo = max(0, p - size + 1) and kept = min(keep, lo): the kept first keys, then the window.
+// A token has kept + p - lo + 1 columns; the matrix's row stride is the most any token of the
+// step can have. Key and value tiles may have different widths (d, dv). All sums are float32
+// and their order depends on the query's own position only, never on the batch. T is float
+// (32-bit path) or __nv_bfloat16; scores, weights and the mix are float32 in both.
+#include "common.cuh"
+
+struct Sight {
+    int lo, kept, n;
+};
+__device__ __forceinline__ Sight sight_of(int p, int size, int keep) {
+    Sight s;
+    s.lo = (size > 0 && p - size + 1 > 0) ? p - size + 1 : 0;
+    s.kept = keep < s.lo ? keep : s.lo;
+    if (s.kept < 0) s.kept = 0;
+    s.n = s.kept + p - s.lo + 1;
+    return s;
+}
+__device__ __forceinline__ int key_of(const Sight& s, int c) { return c < s.kept ? c : s.lo + (c - s.kept); }
+
+__device__ __forceinline__ void load8(const float* p, float* v) {
+    const float4 a = *reinterpret_cast<const float4*>(p), b = *reinterpret_cast<const float4*>(p + 4);
+    v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w; v[4] = b.x; v[5] = b.y; v[6] = b.z; v[7] = b.w;
+}
+__device__ __forceinline__ void load8(const __nv_bfloat16* p, float* v) {
+    const uint4 raw = *reinterpret_cast<const uint4*>(p);
+    const __nv_bfloat162* b = reinterpret_cast<const __nv_bfloat162*>(&raw);
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+        const float2 f = __bfloat1622float2(b[k]);
+        v[2 * k] = f.x;
+        v[2 * k + 1] = f.y;
+    }
+}
+
+// ---------------------------------------------------------------- 1. scores
+// Block (token n, kv head g, chunk of TS_COLS columns). The queries of the kv head's `per`
+// heads lie in shared memory as float32; four lanes share a key (each takes every fourth
+// group of eight values of its row), so a warp walks eight keys at a time.
+#define TS_THREADS 128
+#define TS_COLS 64
+#define TS_MAX_PER 16
+template <typename T>
+__global__ void __launch_bounds__(TS_THREADS)
+talk_scores_kernel(const T* __restrict__ q, const T* __restrict__ kcache, const int* __restrict__ table,
+                   int table_stride, const int* __restrict__ tok_seq, const int* __restrict__ tok_pos,
+                   float* __restrict__ W, int row_stride, int n0, int H, int G, int d, int size, int keep,
+                   float scale, int layout) {
+    extern __shared__ __align__(16) float qs[];   // per * d floats
+    pdl_wait();
+    pdl_trigger();
+    const int n = n0 + blockIdx.x, g = blockIdx.y, c0 = blockIdx.z * TS_COLS;
+    const Sight s = sight_of(tok_pos[n], size, keep);
+    if (c0 >= s.n) return;
+    const int per = H / G;
+    const T* qrow = q + ((size_t)n * H + (size_t)g * per) * d;
+    for (int e = threadIdx.x; e < per * d; e += TS_THREADS) qs[e] = to_f32(qrow[e]);
+    __syncthreads();
+    const int* bt = table + (size_t)tok_seq[n] * table_stride;
+    const int sub = threadIdx.x & 3;
+    const bool vec = (d & 7) == 0 && layout == LUMEN_LAYOUT_LINEAR;
+    for (int cc = threadIdx.x >> 2; cc < TS_COLS; cc += TS_THREADS / 4) {
+        const int c = c0 + cc;
+        const bool live = c < s.n;       // every lane stays for the exchanges below
+        const int j = key_of(s, live ? c : s.n - 1);
+        const T* tile = kcache + ((size_t)bt[j / LUMEN_PAGE] * G + g) * LUMEN_PAGE * d;
+        const int r = j % LUMEN_PAGE;
+        float acc[TS_MAX_PER];
+#pragma unroll
+        for (int hh = 0; hh < TS_MAX_PER; ++hh) acc[hh] = 0.0f;
+        if (vec) {
+            const T* krow = tile + (size_t)r * d;
+            for (int e = sub * 8; e < d; e += 32) {
+                float kv[8];
+                load8(krow + e, kv);
+#pragma unroll
+                for (int hh = 0; hh < TS_MAX_PER; ++hh)
+                    if (hh < per) {
+                        const float* qh = qs + hh * d + e;
+                        float a = acc[hh];
+#pragma unroll
+                        for (int k = 0; k < 8; ++k) a = fmaf(qh[k], kv[k], a);
+                        acc[hh] = a;
+                    }
+            }
+        } else {
+            for (int e = sub; e < d; e += 4) {
+                const float kv = to_f32(tile[tile_offset(layout, r, e, d)]);
+#pragma unroll
+                for (int hh = 0; hh < TS_MAX_PER; ++hh)
+                    if (hh < per) acc[hh] = fmaf(qs[hh * d + e], kv, acc[hh]);
+            }
+        }
+#pragma unroll
+        for (int hh = 0; hh < TS_MAX_PER; ++hh)
+            if (hh < per) {
+                float a = acc[hh];
+                a += __shfl_xor_sync(0xffffffffu, a, 1);
+                a += __shfl_xor_sync(0xffffffffu, a, 2);
+                if (sub == 0 && live) W[((size_t)(n - n0) * H + (size_t)g * per + hh) * row_stride + c] = a * scale;
+            }
+    }
+}
+
+// ---------------------------------------------------------------- 2. softmax and mix
+// Block = token. First every head's maximum and sum over the token's columns (a warp a head),
+// then, 256 columns at a time: every head's weight at the column into shared memory, and from
+// there each output head's mix, written over the scores.
+#define TM_THREADS 256
+#define TM_MAX_H 128
+__global__ void __launch_bounds__(TM_THREADS)
+talk_softmax_mix_kernel(float* __restrict__ W, int row_stride, const int* __restrict__ tok_pos, int n0,
+                        const float* __restrict__ talk, int H, int size, int keep) {
+    extern __shared__ __align__(16) float sm[];   // H * H (talk) + H * TM_THREADS (weights)
+    __shared__ float mx[TM_MAX_H], inv[TM_MAX_H];
+    float* tk = sm;
+    float* ws = sm + H * H;
+    for (int i = threadIdx.x; i < H * H; i += TM_THREADS) tk[i] = talk[i];    // never changes
+    pdl_wait();
+    pdl_trigger();
+    const int n = blockIdx.x;
+    const Sight s = sight_of(tok_pos[n0 + n], size, keep);
+    float* rows = W + (size_t)n * H * row_stride;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    for (int g = warp; g < H; g += TM_THREADS / 32) {
+        const float* row = rows + (size_t)g * row_stride;
+        float m = -INFINITY;
+        for (int c = lane; c < s.n; c += 32) m = fmaxf(m, row[c]);
+        m = warp_max(m);
+        float l = 0.0f;
+        for (int c = lane; c < s.n; c += 32) l += expf(row[c] - m);
+        l = warp_sum(l);
+        if (lane == 0) {
+            mx[g] = m;
+            inv[g] = 1.0f / l;
+        }
+    }
+    __syncthreads();
+    for (int c0 = 0; c0 < s.n; c0 += TM_THREADS) {
+        const int c = c0 + threadIdx.x;
+        if (c < s.n)
+            for (int g = 0; g < H; ++g)
+                ws[g * TM_THREADS + threadIdx.x] = expf(rows[(size_t)g * row_stride + c] - mx[g]) * inv[g];
+        // a thread reads back only what it wrote: no barrier is needed between the two halves
+        if (c < s.n)
+            for (int h = 0; h < H; ++h) {
+                const float* t = tk + h * H;
+                float a = 0.0f;
+                for (int g = 0; g < H; ++g) a = fmaf(t[g], ws[g * TM_THREADS + threadIdx.x], a);
+                rows[(size_t)h * row_stride + c] = a;
+            }
+    }
+}
+
+// ---------------------------------------------------------------- 3. values
+// Block (token n, head h, part z of the columns): eight warps take the part's columns in
+// turn, a lane holds dv / 32 values of the output (up to eight); the warps' sums are added in
+// warp order. With one part the result goes out as T; with several, float32 partial results
+// [part][token][head][dv] that talk_parts_kernel adds in rising order.
+#define TV_THREADS 256
+#define TV_PART 512
+template <typename T>
+__global__ void __launch_bounds__(TV_THREADS)
+talk_values_kernel(const float* __restrict__ W, int row_stride, const T* __restrict__ vcache,
+                   const int* __restrict__ table, int table_stride, const int* __restrict__ tok_seq,
+                   const int* __restrict__ tok_pos, T* __restrict__ out, float* __restrict__ parts, int n0, int n_rows,
+                   int H, int G, int dv, int size, int keep, int layout) {
+    __shared__ float acc_s[TV_THREADS / 32][256];
+    pdl_wait();
+    pdl_trigger();
+    const int n = blockIdx.x, h = blockIdx.y, z = blockIdx.z;
+    const int g = h / (H / G);
+    const Sight s = sight_of(tok_pos[n0 + n], size, keep);
+    const int c_lo = z * TV_PART, c_hi = min(s.n, c_lo + TV_PART);
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int* bt = table + (size_t)tok_seq[n0 + n] * table_stride;
+    const float* row = W + ((size_t)n * H + h) * row_stride;
+    float acc[8];
+#pragma unroll
+    for (int k = 0; k < 8; ++k) acc[k] = 0.0f;
+    for (int c = c_lo + warp; c < c_hi; c += TV_THREADS / 32) {
+        const int j = key_of(s, c);
+        const T* tile = vcache + ((size_t)bt[j / LUMEN_PAGE] * G + g) * LUMEN_PAGE * dv;
+        const int r = j % LUMEN_PAGE;
+        const float w = row[c];
+#pragma unroll
+        for (int k = 0; k < 8; ++k) {
+            const int e = lane + 32 * k;
+            if (e < dv) acc[k] = fmaf(w, to_f32(tile[tile_offset(layout, r, e, dv)]), acc[k]);
+        }
+    }
+#pragma unroll
+    for (int k = 0; k < 8; ++k) acc_s[warp][lane + 32 * k] = acc[k];
+    __syncthreads();
+    for (int e = threadIdx.x; e < dv; e += TV_THREADS) {
+        float a = 0.0f;
+#pragma unroll
+        for (int w8 = 0; w8 < TV_THREADS / 32; ++w8) a += acc_s[w8][e];
+        if (parts) parts[(((size_t)z * n_rows + n) * H + h) * dv + e] = a;
+        else out[((size_t)(n0 + n) * H + h) * dv + e] = from_f32<T>(a);
+    }
+}
+
+template <typename T>
+__global__ void talk_parts_kernel(const float* __restrict__ parts, int Z, size_t part_stride,
+                                  const int* __restrict__ tok_pos, int n0, int row_width, int size, int keep,
+                                  T* __restrict__ out, size_t total) {
+    pdl_wait();
+    pdl_trigger();
+    const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= total) return;
+    const int n = (int)(i / row_width);
+    const Sight s = sight_of(tok_pos[n0 + n], size, keep);
+    const int used = (s.n + TV_PART - 1) / TV_PART;        // parts beyond a token's columns hold zeros
+    float a = 0.0f;
+    for (int z = 0; z < Z && z < used; ++z) a += parts[(size_t)z * part_stride + i];
+    out[(size_t)n0 * row_width + i] = from_f32<T>(a);
+}
+
+// ---------------------------------------------------------------- host side
+// q [N, H, d], out [N, H, dv]; scratch: float32 [rows, H, row_stride] with rows >= min(N,
+// rows_per_pass); parts: float32 [Z, rows, H, dv] when row_stride > TV_PART (Z parts), else null.
+template <typename T>
+static int attn_talk_run(const T* q, const T* kc, const T* vc, const int* table, int table_stride, const int* tok_seq,
+                         const int* tok_pos, const float* talk, T* out, float* W, float* parts, int N,
+                         int rows_per_pass, int row_stride, int H, int G, int d, int dv, int size, int keep,
+                         float scale, int k_layout, int v_layout, cudaStream_t stream) {
+    const int per = H / G;
+    const int chunks = (row_stride + TS_COLS - 1) / TS_COLS;
+    const int Z = (row_stride + TV_PART - 1) / TV_PART;
+    const size_t smem1 = (size_t)per * d * sizeof(float);
+    const size_t smem2 = ((size_t)H * H + (size_t)H * TM_THREADS) * sizeof(float);
+    if (smem1 > 160 * 1024 || smem2 > 200 * 1024) return LUMEN_ERR_UNSUPPORTED;
+    if (smem1 > 48 * 1024)
+        cudaFuncSetAttribute(talk_scores_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem1);
+    if (smem2 > 48 * 1024)
+        cudaFuncSetAttribute(talk_softmax_mix_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem2);
+    for (int n0 = 0; n0 < N; n0 += rows_per_pass) {
+        const int rows = min(rows_per_pass, N - n0);
+        lumen_launch(talk_scores_kernel<T>, dim3(rows, G, chunks), dim3(TS_THREADS), smem1, stream, q, kc, table,
+                     table_stride, tok_seq, tok_pos, W, row_stride, n0, H, G, d, size, keep, scale, k_layout);
+        lumen_launch(talk_softmax_mix_kernel, dim3(rows), dim3(TM_THREADS), smem2, stream, W, row_stride, tok_pos, n0,
+                     talk, H, size, keep);
+        lumen_launch(talk_values_kernel<T>, dim3(rows, H, Z), dim3(TV_THREADS), 0, stream, (const float*)W, row_stride,
+                     vc, table, table_stride, tok_seq, tok_pos, out, Z > 1 ? parts : (float*)nullptr, n0, rows, H, G, dv,
+                     size, keep, v_layout);
+        if (Z > 1) {
+            const size_t total = (size_t)rows * H * dv;
+            lumen_launch(talk_parts_kernel<T>, dim3((unsigned)((total + 255) / 256)), dim3(256), 0, stream,
+                         (const float*)parts, Z, total, tok_pos, n0, H * dv, size, keep, out, total);
+        }
+        cudaError_t e = cudaGetLastError();
+        if (e != cudaSuccess) return (int)e;
+    }
+    return 0;
+}
+
+LUMEN_API int lumen_attn_talk(const void* q, const void* kc, const void* vc, const int* table, int table_stride,
+                              const int* tok_seq, const int* tok_pos, const float* talk, void* out, float* W,
+                              float* parts, int is_bf16, int N, int rows_per_pass, int row_stride, int H, int G, int d,
+                              int dv, int size, int keep, float scale, int k_layout, int v_layout,
+                              cudaStream_t stream) {
+    if (N <= 0) return 0;
+    if (H <= 0 || G <= 0 || H % G || H / G > TS_MAX_PER || H > TM_MAX_H || d <= 0 || dv <= 0 || dv > 256 ||
+        rows_per_pass <= 0 || row_stride <= 0 || size < 0 || keep < 0 || H > 65535)
+        return LUMEN_ERR_UNSUPPORTED;
+    if ((row_stride + TS_COLS - 1) / TS_COLS > 65535) return LUMEN_ERR_UNSUPPORTED;
+    if ((k_layout == LUMEN_LAYOUT_SW128 && (!is_bf16 || d % 64)) || (v_layout == LUMEN_LAYOUT_SW128 && (!is_bf16 || dv % 64)))
+        return LUMEN_ERR_UNSUPPORTED;
+    if (row_stride > TV_PART && !parts) return LUMEN_ERR_BAD_ARGUMENT;
+    if (is_bf16)
+        return attn_talk_run<__nv_bfloat16>((const __nv_bfloat16*)q, (const __nv_bfloat16*)kc, (const __nv_bfloat16*)vc,
+                                            table, table_stride, tok_seq, tok_pos, talk, (__nv_bfloat16*)out, W, parts, N,
+                                            rows_per_pass, row_stride, H, G, d, dv, size, keep, scale, k_layout,
+                                            v_layout, stream);
+    return attn_talk_run<float>((const float*)q, (const float*)kc, (const float*)vc, table, table_stride, tok_seq,
+                                tok_pos, talk, (float*)out, W, parts, N, rows_per_pass, row_stride, H, G, d, dv, size,
+                                keep, scale, k_layout, v_layout, stream);
+}

@@ -1,0 +1,397 @@
+// Row kernels of layers that are arranged otherwise than the plain pre-norm decoder:
+//   - token embedding times a scale plus a learned position vector,
+//   - an update that is RMS-normed BEFORE it joins the residual stream, fused with the norm
+//     of the next sublayer (post-norm + add + pre-norm in one pass over the row),
+//   - a short causal convolution over time on each channel of a sublayer's input, with the
+//     last inputs of every sequence kept as state,
+//   - PolyNorm, an activation made of three unit-RMS powers,
+//   - bias + one RMS norm over the WHOLE query (and key) projection + cache write.
+// All arithmetic is float32; T / TOut is float (32-bit path) or __nv_bfloat16. Inputs that come
+// from a split matrix product arrive as S partial results [S, rows, width] and are added in
+// rising order of S while they are read.
+#include "common.cuh"
+
+__device__ __forceinline__ float ld_f32(const float* p) { return *p; }
+__device__ __forceinline__ float ld_f32(const __nv_bfloat16* p) { return __bfloat162float(*p); }
+
+// ---------------------------------------------------------------- embedding + position
+// h[t, :] = float(E[token[t], :]) * scale + float(P[pos[t], :]). A token or a position outside
+// its table contributes zeros (the host has refused it before; this is the second guard).
+template <typename TW, typename TP>
+__global__ void embed_pos_kernel(const int* __restrict__ tokens, const TW* __restrict__ table, float scale,
+                                 const int* __restrict__ positions, const TP* __restrict__ pos_table, int P,
+                                 float* __restrict__ h, int H, int V) {
+    pdl_trigger();
+    pdl_wait();
+    const int t = blockIdx.x;
+    const int tok = tokens[t];
+    const bool ok = tok >= 0 && tok < V;
+    const TW* row = table + (size_t)(ok ? tok : 0) * H;
+    const int pos = pos_table ? positions[t] : -1;
+    const bool pok = pos >= 0 && pos < P;
+    const TP* prow = pos_table + (size_t)(pok ? pos : 0) * H;
+    float* out = h + (size_t)t * H;
+    for (int i = threadIdx.x; i < H; i += blockDim.x) {
+        float v = ok ? __fmul_rn(ld_f32(row + i), scale) : 0.0f;
+        if (pok) v = __fadd_rn(v, ld_f32(prow + i));
+        out[i] = v;
+    }
+}
+
+// The same from a token table kept in the tiled form of the tensor-core products (piece c, 8
+// values, of row r lies in k block c / 8 at row kb * w_rows + r, place (c & 7) ^ (r & 7)).
+template <typename TP>
+__global__ void embed_pos_tiled_kernel(const int* __restrict__ tokens, const uint4* __restrict__ table, float scale,
+                                       const int* __restrict__ positions, const TP* __restrict__ pos_table, int P,
+                                       float* __restrict__ h, int H, int V, int w_rows) {
+    pdl_trigger();
+    pdl_wait();
+    const int t = blockIdx.x;
+    const int tok = tokens[t];
+    const bool ok = tok >= 0 && tok < V;
+    const int pos = pos_table ? positions[t] : -1;
+    const bool pok = pos >= 0 && pos < P;
+    const TP* prow = pos_table + (size_t)(pok ? pos : 0) * H;
+    float* out = h + (size_t)t * H;
+    for (int c = threadIdx.x; c < H / 8; c += blockDim.x) {
+        float v[8];
+#pragma unroll
+        for (int k = 0; k < 8; ++k) v[k] = 0.0f;
+        if (ok) {
+            const uint4 raw = table[((size_t)(c >> 3) * w_rows + tok) * 8 + ((c & 7) ^ (tok & 7))];
+            const __nv_bfloat16* b = reinterpret_cast<const __nv_bfloat16*>(&raw);
+#pragma unroll
+            for (int k = 0; k < 8; ++k) v[k] = __fmul_rn(__bfloat162float(b[k]), scale);
+        }
+        if (pok) {
+#pragma unroll
+            for (int k = 0; k < 8; ++k) v[k] = __fadd_rn(v[k], ld_f32(prow + 8 * c + k));
+        }
+#pragma unroll
+        for (int k = 0; k < 8; ++k) out[8 * c + k] = v[k];
+    }
+}
+
+LUMEN_API int lumen_embed_pos(const int* tokens, const void* table, int table_is_bf16, int tiled_rows, float scale,
+                              const int* positions, const void* pos_table, int pos_is_bf16, int P, float* h,
+                              int N, int H, int V, cudaStream_t stream) {
+    if (N <= 0) return 0;
+    if (H <= 0 || V <= 0 || (pos_table && (!positions || P <= 0))) return LUMEN_ERR_BAD_ARGUMENT;
+    if (tiled_rows > 0) {
+        if ((H & 7) || tiled_rows < V || (tiled_rows & 7) || ((uintptr_t)table & 15)) return LUMEN_ERR_BAD_ARGUMENT;
+        if (pos_is_bf16)
+            lumen_launch(embed_pos_tiled_kernel<__nv_bfloat16>, dim3(N), dim3(128), 0, stream, tokens, (const uint4*)table,
+                         scale, positions, (const __nv_bfloat16*)pos_table, P, h, H, V, tiled_rows);
+        else
+            lumen_launch(embed_pos_tiled_kernel<float>, dim3(N), dim3(128), 0, stream, tokens, (const uint4*)table, scale,
+                         positions, (const float*)pos_table, P, h, H, V, tiled_rows);
+    } else if (table_is_bf16 && pos_is_bf16) {
+        lumen_launch(embed_pos_kernel<__nv_bfloat16, __nv_bfloat16>, dim3(N), dim3(256), 0, stream, tokens,
+                     (const __nv_bfloat16*)table, scale, positions, (const __nv_bfloat16*)pos_table, P, h, H, V);
+    } else if (table_is_bf16) {
+        lumen_launch(embed_pos_kernel<__nv_bfloat16, float>, dim3(N), dim3(256), 0, stream, tokens,
+                     (const __nv_bfloat16*)table, scale, positions, (const float*)pos_table, P, h, H, V);
+    } else if (pos_is_bf16) {
+        lumen_launch(embed_pos_kernel<float, __nv_bfloat16>, dim3(N), dim3(256), 0, stream, tokens, (const float*)table,
+                     scale, positions, (const __nv_bfloat16*)pos_table, P, h, H, V);
+    } else {
+        lumen_launch(embed_pos_kernel<float, float>, dim3(N), dim3(256), 0, stream, tokens, (const float*)table, scale,
+                     positions, (const float*)pos_table, P, h, H, V);
+    }
+    LUMEN_LAUNCH_CHECK();
+    return 0;
+}
+
+// ---------------------------------------------------------------- post-norm + add + norm
+// u = delta[0][r] + ... + delta[S-1][r] (+ bias);  x = h[r] + u / sqrt(mean(u^2) + eps_u) * wu;
+// if write_h, h[r] = x;  if wn, y[b] = x / sqrt(mean(x^2) + eps_n) * wn.
+// With `rows`, block b reads row rows[b] and writes y row b; without, row b.
+template <typename TOut>
+__global__ void __launch_bounds__(1024)
+postnorm_add_rmsnorm_kernel(float* __restrict__ h, const float* __restrict__ delta, int S, size_t delta_stride,
+                            const float* __restrict__ bias, const float* __restrict__ wu, float eps_u,
+                            const float* __restrict__ wn, float eps_n, TOut* __restrict__ y,
+                            const int* __restrict__ rows, int H, int write_h) {
+    extern __shared__ __align__(16) float xs[];  // H floats
+    __shared__ float red[32];
+    pdl_trigger();
+    pdl_wait();
+    const int b = blockIdx.x;
+    const int r = rows ? rows[b] : b;
+    float* hr = h + (size_t)r * H;
+    const float* dr = delta + (size_t)r * H;
+    float ss = 0.0f;
+    for (int i = threadIdx.x; i < H; i += blockDim.x) {
+        float u = dr[i];
+        for (int s = 1; s < S; ++s) u += dr[(size_t)s * delta_stride + i];
+        if (bias) u += bias[i];
+        xs[i] = u;
+        ss += u * u;
+    }
+    ss = block_sum(ss, red);
+    const float su = 1.0f / sqrtf(ss / (float)H + eps_u);
+    float ss2 = 0.0f;
+    for (int i = threadIdx.x; i < H; i += blockDim.x) {
+        const float x = hr[i] + xs[i] * su * wu[i];
+        xs[i] = x;
+        if (write_h) hr[i] = x;
+        ss2 += x * x;
+    }
+    if (wn == nullptr) return;
+    ss2 = block_sum(ss2, red);
+    const float sn = 1.0f / sqrtf(ss2 / (float)H + eps_n);
+    TOut* yr = y + (size_t)b * H;
+    for (int i = threadIdx.x; i < H; i += blockDim.x) yr[i] = from_f32<TOut>(xs[i] * sn * wn[i]);
+}
+
+static int row_threads(int width, int n_rows) {
+    int t = 256;
+    if (n_rows < 2 * 148) {                      // few rows: wide blocks, all loads of a row in flight
+        t = ((width + 31) / 32) * 32;
+        if (t > 1024) t = 1024;
+        if (t < 128) t = 128;
+    }
+    return t;
+}
+
+LUMEN_API int lumen_postnorm_add_rmsnorm(float* h, const float* delta, int n_delta, long long delta_stride,
+                                         const float* bias, const float* wu, float eps_u, const float* wn,
+                                         float eps_n, void* y, int y_is_bf16, const int* rows, int n_rows, int H,
+                                         int write_h, cudaStream_t stream) {
+    if (n_rows <= 0) return 0;
+    if (H <= 0 || n_delta < 1 || !delta || !wu || (wn && !y)) return LUMEN_ERR_BAD_ARGUMENT;
+    const size_t smem = (size_t)H * sizeof(float);
+    if (smem > 200 * 1024) return LUMEN_ERR_UNSUPPORTED;
+    const int threads = row_threads(H, n_rows);
+    if (y_is_bf16) {
+        auto k = postnorm_add_rmsnorm_kernel<__nv_bfloat16>;
+        if (smem > 48 * 1024) cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        lumen_launch(k, dim3(n_rows), dim3(threads), smem, stream, h, delta, n_delta, (size_t)delta_stride, bias, wu,
+                     eps_u, wn, eps_n, (__nv_bfloat16*)y, rows, H, write_h);
+    } else {
+        auto k = postnorm_add_rmsnorm_kernel<float>;
+        if (smem > 48 * 1024) cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        lumen_launch(k, dim3(n_rows), dim3(threads), smem, stream, h, delta, n_delta, (size_t)delta_stride, bias, wu,
+                     eps_u, wn, eps_n, (float*)y, rows, H, write_h);
+    }
+    LUMEN_LAUNCH_CHECK();
+    return 0;
+}
+
+// ---------------------------------------------------------------- causal convolution of a sublayer's input
+// out[t] = y[t] + sum_{j < taps} w[j] * y[t - taps + 1 + j] on every channel, over the tokens of
+// ONE sequence; what lies before the step's first token comes from the sequence's state (its
+// last taps - 1 inputs, zeros for a new sequence), and the state is moved on to the step's end.
+// w is stored [taps][H]. Blocks [0, N) take one token each and leave at once if the token is
+// among the first taps - 1 of its sequence in this step; blocks [N, N + B) take one sequence
+// each: its first tokens (which read the state) and the state's update, so that whatever
+// touches a sequence's state is read and then written by the same thread.
+#define CANON_MAX_TAPS 16
+template <typename TOut>
+__global__ void canon_conv_kernel(const float* __restrict__ y, const float* __restrict__ w, int taps,
+                                  float* __restrict__ state, size_t slot_stride, const int* __restrict__ tok_seq,
+                                  const int* __restrict__ cu_q, const int* __restrict__ seq_slot, int N, int B,
+                                  TOut* __restrict__ out, int H) {
+    pdl_trigger();
+    pdl_wait();
+    const int blk = blockIdx.x;
+    const int back = taps - 1;
+    if (blk < N) {
+        const int n = blk;
+        const int i = n - cu_q[tok_seq[n]];
+        if (i < back) return;
+        for (int c = threadIdx.x; c < H; c += blockDim.x) {
+            float acc = y[(size_t)n * H + c];
+            for (int j = 0; j < taps; ++j) acc += w[(size_t)j * H + c] * y[(size_t)(n - back + j) * H + c];
+            out[(size_t)n * H + c] = from_f32<TOut>(acc);
+        }
+        return;
+    }
+    const int b = blk - N;
+    const int n0 = cu_q[b], q = cu_q[b + 1] - n0;
+    if (q <= 0 || back == 0) return;
+    float* st = state + (size_t)seq_slot[b] * slot_stride;
+    const int m = q < back ? q : back;
+    for (int c = threadIdx.x; c < H; c += blockDim.x) {
+        float win[CANON_MAX_TAPS];
+#pragma unroll
+        for (int k = 0; k < CANON_MAX_TAPS - 1; ++k) win[k] = k < back ? st[(size_t)k * H + c] : 0.0f;
+        for (int i = 0; i < m; ++i) {
+            const float cur = y[(size_t)(n0 + i) * H + c];
+            float acc = cur;
+#pragma unroll
+            for (int j = 0; j < CANON_MAX_TAPS - 1; ++j)
+                if (j < back) acc += w[(size_t)j * H + c] * win[j];
+            acc += w[(size_t)back * H + c] * cur;
+            out[(size_t)(n0 + i) * H + c] = from_f32<TOut>(acc);
+#pragma unroll
+            for (int k = 0; k < CANON_MAX_TAPS - 2; ++k) win[k] = win[k + 1];
+#pragma unroll
+            for (int k = 0; k < CANON_MAX_TAPS - 1; ++k)
+                if (k == back - 1) win[k] = cur;
+        }
+        if (q >= back) {
+            for (int k = 0; k < back; ++k) st[(size_t)k * H + c] = y[(size_t)(n0 + q - back + k) * H + c];
+        } else {
+#pragma unroll
+            for (int k = 0; k < CANON_MAX_TAPS - 1; ++k)
+                if (k < back) st[(size_t)k * H + c] = win[k];
+        }
+    }
+}
+
+LUMEN_API int lumen_canon_conv(const float* y, const float* w, int taps, float* state, long long slot_stride,
+                               const int* tok_seq, const int* cu_q, const int* seq_slot, int N, int B, void* out,
+                               int out_is_bf16, int H, cudaStream_t stream) {
+    if (N <= 0) return 0;
+    if (H <= 0 || B <= 0 || taps < 1 || taps > CANON_MAX_TAPS || (taps > 1 && !state)) return LUMEN_ERR_UNSUPPORTED;
+    const int threads = H >= 1024 ? 256 : 128;
+    if (out_is_bf16)
+        lumen_launch(canon_conv_kernel<__nv_bfloat16>, dim3(N + B), dim3(threads), 0, stream, y, w, taps, state,
+                     (size_t)slot_stride, tok_seq, cu_q, seq_slot, N, B, (__nv_bfloat16*)out, H);
+    else
+        lumen_launch(canon_conv_kernel<float>, dim3(N + B), dim3(threads), 0, stream, y, w, taps, state,
+                     (size_t)slot_stride, tok_seq, cu_q, seq_slot, N, B, (float*)out, H);
+    LUMEN_LAUNCH_CHECK();
+    return 0;
+}
+
+// ---------------------------------------------------------------- PolyNorm
+// out = a z / rms(z) + b z^2 / rms(z^2) + c z^3 / rms(z^3) + e, powers element by element,
+// rms(v) = sqrt(mean(v^2) + eps) over the row; act = (a, b, c, e) on the device.
+template <typename TOut>
+__global__ void __launch_bounds__(1024)
+polynorm_kernel(const float* __restrict__ z, int S, size_t split_stride, const float* __restrict__ act, float eps,
+                TOut* __restrict__ out, int F) {
+    extern __shared__ __align__(16) float xs[];  // F floats
+    __shared__ float red[32];
+    pdl_trigger();
+    pdl_wait();
+    const size_t row = blockIdx.x;
+    const float* zr = z + row * F;
+    float s2 = 0.0f, s4 = 0.0f, s6 = 0.0f;
+    for (int i = threadIdx.x; i < F; i += blockDim.x) {
+        float v = zr[i];
+        for (int s = 1; s < S; ++s) v += zr[(size_t)s * split_stride + i];
+        xs[i] = v;
+        const float v2 = v * v;
+        s2 += v2;
+        s4 += v2 * v2;
+        s6 += v2 * v2 * v2;
+    }
+    s2 = block_sum(s2, red);
+    s4 = block_sum(s4, red);
+    s6 = block_sum(s6, red);
+    const float r1 = 1.0f / sqrtf(s2 / (float)F + eps), r2 = 1.0f / sqrtf(s4 / (float)F + eps),
+                r3 = 1.0f / sqrtf(s6 / (float)F + eps);
+    const float a = act[0], b = act[1], c = act[2], e = act[3];
+    TOut* orow = out + row * F;
+    for (int i = threadIdx.x; i < F; i += blockDim.x) {
+        const float v = xs[i], v2 = v * v;
+        orow[i] = from_f32<TOut>(a * (v * r1) + b * (v2 * r2) + c * (v2 * v * r3) + e);
+    }
+}
+
+LUMEN_API int lumen_polynorm(const float* z, int n_split, long long split_stride, const float* act, float eps,
+                             void* out, int out_is_bf16, int N, int F, cudaStream_t stream) {
+    if (N <= 0) return 0;
+    if (F <= 0 || n_split < 1 || !act) return LUMEN_ERR_BAD_ARGUMENT;
+    const size_t smem = (size_t)F * sizeof(float);
+    if (smem > 200 * 1024) return LUMEN_ERR_UNSUPPORTED;
+    const int threads = row_threads(F, N);
+    if (out_is_bf16) {
+        auto k = polynorm_kernel<__nv_bfloat16>;
+        if (smem > 48 * 1024) cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        lumen_launch(k, dim3(N), dim3(threads), smem, stream, z, n_split, (size_t)split_stride, act, eps,
+                     (__nv_bfloat16*)out, F);
+    } else {
+        auto k = polynorm_kernel<float>;
+        if (smem > 48 * 1024) cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        lumen_launch(k, dim3(N), dim3(threads), smem, stream, z, n_split, (size_t)split_stride, act, eps, (float*)out, F);
+    }
+    LUMEN_LAUNCH_CHECK();
+    return 0;
+}
+
+// ---------------------------------------------------------------- bias + whole-projection norm + cache write
+// A row of the stacked projection holds Wq query values, Wk key values and Wv value values.
+// x = sum of the partials + bias; the query part is divided by its root mean square over ALL
+// Wq values (all heads at once) and multiplied by qw [Wq], the key part likewise with kw [Wk]
+// (a null weight leaves the part as it is); q goes out as [N, Wq], the key and the value of
+// the token to its place in the paged cache: key tiles [page][kv head][PAGE][d], value tiles
+// [page][kv head][PAGE][dv].
+template <typename T>
+__global__ void __launch_bounds__(1024)
+qkv_bias_norm_store_kernel(const float* __restrict__ qkv, int S, size_t split_stride, const float* __restrict__ bias,
+                           const float* __restrict__ qw, const float* __restrict__ kw, float eps,
+                           const int* __restrict__ cache_pos, const int* __restrict__ tok_seq,
+                           const int* __restrict__ table, int table_stride, T* __restrict__ q_out,
+                           T* __restrict__ kc, T* __restrict__ vc, int Wq, int Wk, int Wv, int G, int d, int dv,
+                           int k_layout, int v_layout) {
+    extern __shared__ __align__(16) float xs[];  // Wq + Wk + Wv floats
+    __shared__ float red[32];
+    pdl_trigger();
+    pdl_wait();
+    const int n = blockIdx.x;
+    const int W = Wq + Wk + Wv;
+    const float* row = qkv + (size_t)n * W;
+    float sq = 0.0f, sk = 0.0f;
+    for (int i = threadIdx.x; i < W; i += blockDim.x) {
+        float x = row[i];
+        for (int s = 1; s < S; ++s) x += row[(size_t)s * split_stride + i];
+        if (bias) x += bias[i];
+        xs[i] = x;
+        if (i < Wq) sq += x * x;
+        else if (i < Wq + Wk) sk += x * x;
+    }
+    sq = block_sum(sq, red);
+    sk = block_sum(sk, red);
+    const float rq = qw ? 1.0f / sqrtf(sq / (float)Wq + eps) : 1.0f;
+    const float rk = kw ? 1.0f / sqrtf(sk / (float)Wk + eps) : 1.0f;
+    const int pos = cache_pos[n];
+    const int page = table[(size_t)tok_seq[n] * table_stride + pos / LUMEN_PAGE];
+    const int r = pos % LUMEN_PAGE;
+    for (int i = threadIdx.x; i < W; i += blockDim.x) {
+        const float x = xs[i];
+        if (i < Wq) {
+            q_out[(size_t)n * Wq + i] = from_f32<T>(qw ? x * rq * qw[i] : x);
+        } else if (i < Wq + Wk) {
+            const int e = i - Wq, g = e / d, ee = e - g * d;
+            kc[((size_t)page * G + g) * LUMEN_PAGE * d + tile_offset(k_layout, r, ee, d)] =
+                from_f32<T>(kw ? x * rk * kw[e] : x);
+        } else {
+            const int e = i - Wq - Wk, g = e / dv, ee = e - g * dv;
+            vc[((size_t)page * G + g) * LUMEN_PAGE * dv + tile_offset(v_layout, r, ee, dv)] = from_f32<T>(x);
+        }
+    }
+}
+
+LUMEN_API int lumen_qkv_bias_norm_store(const float* qkv, int n_split, long long split_stride, const float* bias,
+                                        const float* qw, const float* kw, float eps, const int* cache_pos,
+                                        const int* tok_seq, const int* table, int table_stride, void* q_out,
+                                        void* kc, void* vc, int is_bf16, int N, int Wq, int G, int d, int dv,
+                                        int k_layout, int v_layout, cudaStream_t stream) {
+    if (N <= 0) return 0;
+    if (Wq <= 0 || G <= 0 || d <= 0 || dv <= 0 || n_split < 1) return LUMEN_ERR_BAD_ARGUMENT;
+    if ((k_layout == LUMEN_LAYOUT_SW128 && (!is_bf16 || d % 64)) || (v_layout == LUMEN_LAYOUT_SW128 && (!is_bf16 || dv % 64)))
+        return LUMEN_ERR_UNSUPPORTED;
+    const int Wk = G * d, Wv = G * dv, W = Wq + Wk + Wv;
+    const size_t smem = (size_t)W * sizeof(float);
+    if (smem > 200 * 1024) return LUMEN_ERR_UNSUPPORTED;
+    const int threads = row_threads(W, N);
+    if (is_bf16) {
+        auto k = qkv_bias_norm_store_kernel<__nv_bfloat16>;
+        if (smem > 48 * 1024) cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        lumen_launch(k, dim3(N), dim3(threads), smem, stream, qkv, n_split, (size_t)split_stride, bias, qw, kw, eps,
+                     cache_pos, tok_seq, table, table_stride, (__nv_bfloat16*)q_out, (__nv_bfloat16*)kc,
+                     (__nv_bfloat16*)vc, Wq, Wk, Wv, G, d, dv, k_layout, v_layout);
+    } else {
+        auto k = qkv_bias_norm_store_kernel<float>;
+        if (smem > 48 * 1024) cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        lumen_launch(k, dim3(N), dim3(threads), smem, stream, qkv, n_split, (size_t)split_stride, bias, qw, kw, eps,
+                     cache_pos, tok_seq, table, table_stride, (float*)q_out, (float*)kc, (float*)vc, Wq, Wk, Wv, G, d,
+                     dv, k_layout, v_layout);
+    }
+    LUMEN_LAUNCH_CHECK();
+    return 0;
+}

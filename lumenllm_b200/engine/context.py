@@ -96,11 +96,16 @@ class EntryView:
         """Tile layout of this run's cache pages (cache.kv.LAYOUT_*)."""
         return self.ctx.cache.groups[self.ctx.cache.group_of[self.cache_entry]].layout
 
-    def state(self):
+    @property
+    def v_layout(self) -> int:
+        """Tile layout of this run's value pages (they may be of another width than the keys')."""
+        return self.ctx.cache.groups[self.ctx.cache.group_of[self.cache_entry]].v_layout
+
+    def state(self, name: str = "mixer"):
         """Per-sequence state of fixed size: [max_slots + 1, *shape]; row seq_slot[b] belongs
-        to sequence b (the last row to every padding sequence). None if the mixer declared
-        none."""
-        return self.ctx.cache.state.of(self.entry)
+        to sequence b (the last row to every padding sequence). "mixer" is the mixer's,
+        "block" the block arrangement's own. None if none was declared."""
+        return self.ctx.cache.state.of(self.entry, name)
 
 
 @dataclass

@@ -44,8 +44,9 @@ class DecoderModel:
         self.schedule = spec.schedule
         # a step can be captured in a CUDA graph only if no part looks at the step's
         # host-side lists; parts say so with `graph_safe = True`
-        self.graph_safe = all(getattr(b.mixer, "graph_safe", False) and
-                              getattr(b.ffn, "graph_safe", False) for b in self.blocks)
+        self.graph_safe = all(b.graph_safe if hasattr(b, "graph_safe") else
+                              (getattr(b.mixer, "graph_safe", False) and getattr(b.ffn, "graph_safe", False))
+                              for b in self.blocks)
 
     # what the cache must hold, per schedule entry
     def cache_needs(self) -> Dict[int, CacheNeed]:
@@ -60,15 +61,20 @@ class DecoderModel:
     def state_shapes(self):
         shapes = {}
         for i, e in enumerate(self.schedule):
-            s = self.blocks[e.layer].mixer.state_shape()
+            block = self.blocks[e.layer]
+            s = block.mixer.state_shape()
             if s is not None:
-                shapes[i] = s
+                shapes[(i, "mixer")] = s
+            own = getattr(block, "state_shape", None)       # a block arrangement's own state
+            s = own() if own else None
+            if s is not None:
+                shapes[(i, "block")] = s
         return shapes
 
     def forward(self, ctx: StepContext) -> torch.Tensor:
         """Logits float32 [W, V] at ctx.want_rows."""
         ctx.extras.pop("per_step", None)     # tables that parts share within ONE step
-        h = self.embedding.forward(ctx.tokens)
+        h = self.embedding.forward(ctx.tokens, ctx)
         pending = None
         needs = ctx.cache.group_of
         for i, e in enumerate(self.schedule):

@@ -37,7 +37,9 @@ def main(argv=None) -> int:
     from .engine import Engine, StepEntry
     out = Path(args.out)
     out.mkdir(parents=True, exist_ok=True)
-    engine = Engine.from_folder(args.model, dtype=args.dtype, max_tokens=args.max_tokens)
+    # tensors that no part of the model reads are reported, not refused: a replay is about the
+    # tensors that are read
+    engine = Engine.from_folder(args.model, dtype=args.dtype, max_tokens=args.max_tokens, strict_weights=False)
     slots = {}
     for line in sys.stdin:
         line = line.strip()

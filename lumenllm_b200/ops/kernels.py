@@ -62,6 +62,178 @@ def embed(tokens, table, out=None):
     return out
 
 
+def embed_pos(tokens, table, scale, positions, pos_table, out=None):
+    """h[t] = float32(table[tokens[t]]) * scale + float32(pos_table[positions[t]]) (no position
+    term with pos_table None). table [V, H] float32|bfloat16 or a TiledWeight; pos_table [P, H]
+    float32|bfloat16; tokens, positions int32 [N]."""
+    require(tokens, I32, "embed_pos.tokens")
+    N = tokens.numel()
+    V, H = table.shape
+    tiled = isinstance(table, TiledWeight)
+    data = table.data if tiled else table
+    if not tiled and (not table.is_contiguous() or not table.is_cuda):
+        raise KernelError("embed_pos.table must be a contiguous CUDA tensor")
+    P_rows = 0
+    if pos_table is not None:
+        require(positions, I32, "embed_pos.positions")
+        if pos_table.dim() != 2 or pos_table.shape[1] != H or not pos_table.is_contiguous() or positions.numel() < N:
+            raise KernelError(f"embed_pos: the position table must be [P, {H}], one position a token")
+        P_rows = pos_table.shape[0]
+    if out is None:
+        out = torch.empty((N, H), dtype=F32, device=data.device)
+    f = fn("layer_ops", "lumen_embed_pos", [P, P, c_int, c_int, c_float, P, P, c_int, c_int, P, c_int, c_int, c_int, P])
+    check(f(ptr(tokens), ptr(data), 1 if tiled else _is_bf16(table), table.padded_rows if tiled else 0, float(scale),
+            ptr(positions) if pos_table is not None else 0, ptr(pos_table),
+            _is_bf16(pos_table) if pos_table is not None else 0, P_rows, ptr(out), N, H, V, stream_ptr()), "embed_pos")
+    return out
+
+
+def postnorm_add_rmsnorm(h, delta, bias, w_update, eps_update, w_next, eps_next, out_dtype, rows=None,
+                         write_h=True):
+    """u = sum(delta[s]) (+ bias); x = h + rmsnorm(u) * w_update (stored back to h when write_h);
+    y = rmsnorm(x) * w_next in out_dtype (None with w_next None). h float32 [N, H]; delta float32
+    [N, H] or [S, N, H]; rows int32 [W] gathers the rows to work on."""
+    require(h, F32, "postnorm_add_rmsnorm.h")
+    require(w_update, F32, "postnorm_add_rmsnorm.w_update")
+    N, H = h.shape
+    delta, S = _partials(delta, "postnorm_add_rmsnorm.delta")
+    if tuple(delta.shape[1:]) != (N, H) or w_update.numel() != H:
+        raise KernelError(f"postnorm_add_rmsnorm: delta {tuple(delta.shape)} / weight do not match h {(N, H)}")
+    for t, nm in ((bias, "bias"), (w_next, "w_next")):
+        if t is not None:
+            require(t, F32, f"postnorm_add_rmsnorm.{nm}")
+            if t.numel() != H:
+                raise KernelError(f"postnorm_add_rmsnorm: {nm} has {t.numel()} values, rows have {H}")
+    n_rows = N
+    if rows is not None:
+        require(rows, I32, "postnorm_add_rmsnorm.rows")
+        n_rows = rows.numel()
+    y = torch.empty((n_rows, H), dtype=out_dtype, device=h.device) if w_next is not None else None
+    f = fn("layer_ops", "lumen_postnorm_add_rmsnorm",
+           [P, P, c_int, c_longlong, P, P, c_float, P, c_float, P, c_int, P, c_int, c_int, c_int, P])
+    check(f(ptr(h), ptr(delta), S, N * H, ptr(bias), ptr(w_update), float(eps_update), ptr(w_next), float(eps_next),
+            ptr(y), _is_bf16(y) if y is not None else 0, ptr(rows), n_rows, H, 1 if write_h else 0, stream_ptr()),
+          "postnorm_add_rmsnorm")
+    return y
+
+
+CANON_MAX_TAPS = 16
+
+
+def canon_conv(y, weight, state, tok_seq, cu_q, seq_slot, n_seqs, out_dtype):
+    """out_t = y_t + sum_j weight[j] * y_(t - taps + 1 + j) per channel within each sequence of the
+    step; inputs before the step's first token come from `state` (float32 [slots, taps - 1, H],
+    possibly a view with a larger slot stride), which is moved on to the step's end.
+    y float32 [N, H]; weight float32 [taps, H]."""
+    require(y, F32, "canon_conv.y")
+    require(weight, F32, "canon_conv.weight")
+    N, H = y.shape
+    taps = weight.shape[0]
+    if weight.shape[1] != H or not 1 <= taps <= CANON_MAX_TAPS:
+        raise KernelError(f"canon_conv: weight {tuple(weight.shape)} does not fit rows of {H} (1 to {CANON_MAX_TAPS} taps)")
+    stride = 0
+    if taps > 1:
+        if state is None or state.dtype != F32 or not state.is_cuda or tuple(state.shape[1:]) != (taps - 1, H) \
+                or state.stride(2) != 1 or state.stride(1) != H:
+            raise KernelError(f"canon_conv: state must be float32 [slots, {taps - 1}, {H}] with dense rows")
+        stride = state.stride(0)
+    for t, nm in ((tok_seq, "tok_seq"), (cu_q, "cu_q"), (seq_slot, "seq_slot")):
+        require(t, I32, f"canon_conv.{nm}")
+    out = torch.empty((N, H), dtype=out_dtype, device=y.device)
+    f = fn("layer_ops", "lumen_canon_conv", [P, P, c_int, P, c_longlong, P, P, P, c_int, c_int, P, c_int, c_int, P])
+    check(f(ptr(y), ptr(weight), taps, ptr(state) if taps > 1 else 0, stride, ptr(tok_seq), ptr(cu_q), ptr(seq_slot),
+            N, int(n_seqs), ptr(out), _is_bf16(out), H, stream_ptr()), "canon_conv")
+    return out
+
+
+def polynorm(z, act, eps, out_dtype):
+    """a N(z) + b N(z^2) + c N(z^3) + e with N(v) = v / sqrt(mean(v^2) + eps) over a row and
+    act = (a, b, c, e) float32 on the device; z float32 [N, F] or [S, N, F] partials."""
+    z, S = _partials(z, "polynorm.z")
+    require(act, F32, "polynorm.act")
+    if act.numel() != 4:
+        raise KernelError("polynorm: act holds four values")
+    _, N, Fw = z.shape
+    out = torch.empty((N, Fw), dtype=out_dtype, device=z.device)
+    f = fn("layer_ops", "lumen_polynorm", [P, c_int, c_longlong, P, c_float, P, c_int, c_int, c_int, P])
+    check(f(ptr(z), S, N * Fw, ptr(act), float(eps), ptr(out), _is_bf16(out), N, Fw, stream_ptr()), "polynorm")
+    return out
+
+
+def qkv_bias_norm_store(qkv, bias, q_norm_w, k_norm_w, eps, cache_pos, tok_seq, block_table, kcache, vcache,
+                        nq, nkv, d, dv, out_dtype, k_layout=LAYOUT_LINEAR, v_layout=LAYOUT_LINEAR):
+    """Bias, one RMS norm over the WHOLE query projection (weight [nq * d]) and one over the whole
+    key projection (weight [nkv * d]), q out as [N, nq, d], k and v written to the paged cache
+    (keys [pages, nkv, PAGE, d], values [pages, nkv, PAGE, dv]).
+    qkv float32 [N, nq*d + nkv*d + nkv*dv] or [S, N, ...] partials; bias float32 of that width or None."""
+    qkv, S = _partials(qkv, "qkv_bias_norm_store.qkv")
+    N = qkv.shape[1]
+    width = nq * d + nkv * d + nkv * dv
+    if qkv.shape[2] != width:
+        raise KernelError(f"qkv_bias_norm_store: row width {qkv.shape[2]} != {width}")
+    for t, nm, n in ((bias, "bias", width), (q_norm_w, "q_norm", nq * d), (k_norm_w, "k_norm", nkv * d)):
+        if t is not None:
+            require(t, F32, f"qkv_bias_norm_store.{nm}")
+            if t.numel() != n:
+                raise KernelError(f"qkv_bias_norm_store: {nm} must have {n} values")
+    for t, nm in ((cache_pos, "cache_pos"), (tok_seq, "tok_seq")):
+        require(t, I32, nm)
+        if t.numel() < N:
+            raise KernelError(f"{nm} shorter than the token count")
+    require(block_table, I32, "block_table")
+    require(kcache, out_dtype, "kcache")
+    require(vcache, out_dtype, "vcache")
+    if tuple(kcache.shape[1:]) != (nkv, PAGE, d) or tuple(vcache.shape[1:]) != (nkv, PAGE, dv):
+        raise KernelError(f"qkv_bias_norm_store: caches {tuple(kcache.shape)}, {tuple(vcache.shape)} do not fit "
+                          f"{nkv} kv heads of {d} and {dv}")
+    q_out = torch.empty((N, nq, d), dtype=out_dtype, device=qkv.device)
+    f = fn("layer_ops", "lumen_qkv_bias_norm_store",
+           [P, c_int, c_longlong, P, P, P, c_float, P, P, P, c_int, P, P, P, c_int, c_int, c_int, c_int, c_int, c_int,
+            c_int, c_int, P])
+    check(f(ptr(qkv), S, N * width, ptr(bias), ptr(q_norm_w), ptr(k_norm_w), float(eps), ptr(cache_pos), ptr(tok_seq),
+            ptr(block_table), block_table.stride(0), ptr(q_out), ptr(kcache), ptr(vcache), _is_bf16(q_out), N, nq * d,
+            nkv, d, dv, int(k_layout), int(v_layout), stream_ptr()), "qkv_bias_norm_store")
+    return q_out
+
+
+ATTN_TALK_SCRATCH_BYTES = 256 << 20     # weights matrix of one pass over a step's tokens
+ATTN_TALK_PART = 512                    # columns a block of the values kernel walks (TV_PART)
+
+
+def attn_talk(q, kcache, vcache, block_table, tok_seq, tok_pos, talk, window, keep_first, scale, dv,
+              k_layout=LAYOUT_LINEAR, v_layout=LAYOUT_LINEAR, prompt=False):
+    """Attention with softmax weights mixed across heads (talk float32 [nq, nq]) before they meet
+    the values, over the paged cache; a query at position p sees key j <= p if p - j < window
+    (window 0: every key) or j < keep_first. q [N, nq, d]; keys [pages, nkv, PAGE, d]; values
+    [pages, nkv, PAGE, dv]; returns [N, nq, dv] in q's type."""
+    N, nq, d = q.shape
+    nkv = kcache.shape[1]
+    require(q, q.dtype, "attn_talk.q")
+    require(kcache, q.dtype, "attn_talk.kcache")
+    require(vcache, q.dtype, "attn_talk.vcache")
+    require(block_table, I32, "attn_talk.block_table")
+    require(tok_seq, I32, "attn_talk.tok_seq")
+    require(tok_pos, I32, "attn_talk.tok_pos")
+    require(talk, F32, "attn_talk.talk")
+    if tuple(talk.shape) != (nq, nq) or kcache.shape[3] != d or tuple(vcache.shape[1:]) != (nkv, PAGE, dv):
+        raise KernelError(f"attn_talk: talk {tuple(talk.shape)}, keys {tuple(kcache.shape)}, values "
+                          f"{tuple(vcache.shape)} do not fit {nq} heads of {d} / {dv}")
+    bound = block_table.shape[1] * PAGE           # no sequence of the step is longer than its page table
+    row_stride = max(1, min(int(window) + int(keep_first), bound) if window > 0 else bound)
+    rows_per_pass = max(1, min(N, ATTN_TALK_SCRATCH_BYTES // (nq * row_stride * 4)))
+    out = torch.empty((N, nq, dv), dtype=q.dtype, device=q.device)
+    W = torch.empty((rows_per_pass, nq, row_stride), dtype=F32, device=q.device)
+    Z = -(-row_stride // ATTN_TALK_PART)
+    parts = torch.empty((Z, rows_per_pass, nq, dv), dtype=F32, device=q.device) if Z > 1 else None
+    f = fn("attn_talk", "lumen_attn_talk",
+           [P, P, P, P, c_int, P, P, P, P, P, P, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
+            c_float, c_int, c_int, P])
+    check(f(ptr(q), ptr(kcache), ptr(vcache), ptr(block_table), block_table.stride(0), ptr(tok_seq), ptr(tok_pos),
+            ptr(talk), ptr(out), ptr(W), ptr(parts), _is_bf16(q), N, rows_per_pass, row_stride, nq, nkv, d, dv,
+            int(window), int(keep_first), float(scale), int(k_layout), int(v_layout), stream_ptr()), "attn_talk")
+    return out
+
+
 def add_rmsnorm(h, delta, weight, eps, out_dtype, rows=None, write_h=True):
     """x = h + sum(delta[s]) ; y = rmsnorm(x) * weight. h float32 [N, H] (updated in
     place when write_h); delta None or float32 [S, N, H]; rows int32 [W] gathers."""

@@ -15,7 +15,10 @@ in the constructor and declare their tensors with a classmethod
              which hands out this run's cache pages and per-sequence state)
   ffn        forward(y, ctx) -> delta float32 [S, N, H]
   block      forward(h, pending, ctx, entry) -> (h, pending): how mixer, ffn and
-             norms are arranged around the residual stream
+             norms are arranged around the residual stream; a block with state of its own
+             offers state_shape() -> (shape, dtype) | None like a mixer (EntryView.state("block"))
+  input_conv forward(y, state, ctx, out_dtype) -> what a sublayer reads instead of y
+             (y: float32 normed rows; state: the sequences' last inputs, moved on by the call)
   head       forward(y) -> logits float32 [W, V]
 
 A delta is a list of S partial sums of one update of the residual stream; the
@@ -35,7 +38,7 @@ import torch
 from ..config.spec import ConfigError, PartSpec
 
 _REGISTRY: Dict[Tuple[str, str], type] = {}
-CATEGORIES = ("embedding", "norm", "position", "mixer", "ffn", "block", "head")
+CATEGORIES = ("embedding", "norm", "position", "mixer", "ffn", "block", "head", "input_conv")
 
 
 def register_part(category: str, kind: str) -> Callable[[type], type]:
@@ -75,6 +78,12 @@ class Runtime:
     @property
     def is_f32(self) -> bool:
         return self.dtype == torch.float32
+
+
+def tensor_name(spec: PartSpec, suffix: str = ".weight") -> str:
+    """Where a part's one tensor lives: `params["tensor"]` names it outright (checkpoints whose
+    tensors are not called <prefix>.weight), else prefix + suffix."""
+    return spec.params.get("tensor") or f"{spec.prefix}{suffix}"
 
 
 def need(params: dict, key: str, what: str):

@@ -5,10 +5,19 @@
 The adds are not done here: a block hands its last update on as `pending`, and
 the next norm (the next block's, or the model's final one) adds it while it
 reads the stream anyway.
+
+"sandwich_conv": r = h + norm_b(mixer(conv(norm_a(h)))); h' = r + norm_d(ffn(conv(norm_c(r)))):
+a norm before and after each sublayer, and a short causal convolution over time of what each
+sublayer reads (parts/conv.py), whose last inputs are the block's per-sequence state. The second
+half is left out for a layer without a feed-forward. A sublayer's update is handed on as a
+NormedUpdate, so that its norm, the add and the next sublayer's norm are one kernel.
 """
 from __future__ import annotations
 
+import torch
+
 from .base import build_part, part_tensors, register_part
+from .norm import NormedUpdate
 
 
 @register_part("block", "pre_norm")
@@ -44,3 +53,57 @@ class PreNormBlock:
         else:
             m = self.ffn.forward(y2, ctx)
         return h, m
+
+
+@register_part("block", "sandwich_conv")
+class SandwichConvBlock:
+    @classmethod
+    def tensors(cls, layer_spec):
+        t = {}
+        for name in ("mixer", "mixer_out") + (("ffn", "ffn_out") if layer_spec.ffn is not None else ()):
+            t.update(part_tensors("norm", layer_spec.norms[name]))
+        t.update(part_tensors("input_conv", layer_spec.extras["mixer_conv"]))
+        t.update(part_tensors("mixer", layer_spec.mixer))
+        if layer_spec.ffn is not None:
+            t.update(part_tensors("input_conv", layer_spec.extras["ffn_conv"]))
+            t.update(part_tensors("ffn", layer_spec.ffn))
+        return t
+
+    def __init__(self, layer_spec, weights, runtime):
+        self.runtime = runtime
+        norm = lambda name: build_part("norm", layer_spec.norms[name], weights, runtime)
+        self.norm_mixer, self.norm_mixer_out = norm("mixer"), norm("mixer_out")
+        self.conv_mixer = build_part("input_conv", layer_spec.extras["mixer_conv"], weights, runtime)
+        self.mixer = build_part("mixer", layer_spec.mixer, weights, runtime)
+        self.ffn = None
+        if layer_spec.ffn is not None:
+            self.norm_ffn, self.norm_ffn_out = norm("ffn"), norm("ffn_out")
+            self.conv_ffn = build_part("input_conv", layer_spec.extras["ffn_conv"], weights, runtime)
+            self.ffn = build_part("ffn", layer_spec.ffn, weights, runtime)
+        self.convs = [self.conv_mixer] + ([self.conv_ffn] if self.ffn is not None else [])
+        self.width = self.norm_mixer.size
+
+    @property
+    def graph_safe(self):
+        return all(getattr(p, "graph_safe", False) for p in [self.mixer] + ([self.ffn] if self.ffn else []))
+
+    def state_shape(self):
+        """The convolutions' last inputs: one [taps - 1, width] piece a sublayer, float32."""
+        rows = sum(c.state_rows() for c in self.convs)
+        return ((rows, self.width), torch.float32) if rows else None
+
+    def forward(self, h, pending, ctx, entry):
+        state = entry.state("block")
+        r1 = self.conv_mixer.state_rows()
+        y = self.norm_mixer.forward(h, pending, torch.float32)
+        x = self.conv_mixer.forward(y, None if state is None or not r1 else state[:, :r1], ctx, self.runtime.dtype)
+        a = self.mixer.forward(x, ctx, entry, bias_downstream=True)
+        update = NormedUpdate(a, self.norm_mixer_out.weight, self.norm_mixer_out.eps,
+                              getattr(self.mixer, "update_bias", None))
+        if self.ffn is None:
+            return h, update
+        y = self.norm_ffn.forward(h, update, torch.float32)
+        x = self.conv_ffn.forward(y, None if state is None or not self.conv_ffn.state_rows() else state[:, r1:],
+                                  ctx, self.runtime.dtype)
+        m = self.ffn.forward(x, ctx)
+        return h, NormedUpdate(m, self.norm_ffn_out.weight, self.norm_ffn_out.eps)

@@ -8,20 +8,27 @@ Head: logits = y W^T in float32, with W the embedding table when the head is tie
 from __future__ import annotations
 
 from ..ops import kernels as K
-from .base import need, register_part
+from .base import need, register_part, tensor_name
 from .linear import Linear, tiled_form
 
 
 @register_part("embedding", "token_embedding")
 class TokenEmbedding:
+    """`scale` multiplies the token's vector; `position_tensor` names a learned table
+    [max_positions, hidden] whose row at the token's position is added (not scaled)."""
+
     @classmethod
     def tensors(cls, spec):
-        return {f"{spec.prefix}.weight": ((int(need(spec.params, "vocab_size", "embedding")),
-                                           int(need(spec.params, "hidden_size", "embedding"))),
-                                          "matrix")}
+        H = int(need(spec.params, "hidden_size", "embedding"))
+        t = {tensor_name(spec): ((int(need(spec.params, "vocab_size", "embedding")), H), "matrix")}
+        if spec.params.get("position_tensor"):
+            t[spec.params["position_tensor"]] = ((int(need(spec.params, "max_positions", "embedding")), H), "matrix")
+        return t
 
     def __init__(self, spec, weights, runtime):
-        self.table = weights[f"{spec.prefix}.weight"].contiguous()
+        self.table = weights[tensor_name(spec)].contiguous()
+        pos = spec.params.get("position_tensor")
+        self.positions = weights[pos].contiguous() if pos else None
         self.vocab_size = self.table.shape[0]
         # in a bfloat16 run the table is kept in the form an output head would read it in, so
         # that a head tied to it shares the one copy
@@ -29,11 +36,15 @@ class TokenEmbedding:
             self.table = tiled_form(self.table)
         self.scale = spec.params.get("scale")
 
-    def forward(self, tokens):
-        h = K.embed(tokens, self.table)
+    def forward(self, tokens, ctx=None):
+        if self.positions is not None:
+            if ctx is None:
+                raise ValueError("an embedding with learned positions needs the step's positions")
+            return K.embed_pos(tokens, self.table, 1.0 if self.scale is None else float(self.scale),
+                               ctx.rope_pos, self.positions)
         if self.scale is not None:
-            h.mul_(float(self.scale))
-        return h
+            return K.embed_pos(tokens, self.table, float(self.scale), None, None)
+        return K.embed(tokens, self.table)
 
 
 @register_part("head", "linear_head")
@@ -46,6 +57,8 @@ class LinearHead:
 
     @classmethod
     def tensors(cls, spec):
+        if not spec.params.get("own_tensor", True):        # the head IS the tied table: no tensor of its own
+            return {}
         shape = (int(need(spec.params, "vocab_size", "head")), int(need(spec.params, "hidden_size", "head")))
         return {f"{spec.prefix}.weight": (shape, "optional" if spec.params.get("tied_to") else "matrix")}
 
@@ -56,7 +69,7 @@ class LinearHead:
 
     def __init__(self, spec, weights, runtime):
         own = f"{spec.prefix}.weight"
-        name = own if own in weights else spec.params.get("tied_to")
+        name = own if spec.params.get("own_tensor", True) and own in weights else spec.params.get("tied_to")
         if name is None or name not in weights:
             raise KeyError(f"the output head needs '{own}'")
         self.proj = Linear(weights[name], runtime)

@@ -7,6 +7,11 @@ are interleaved (gate_0, up_0, gate_1, up_1, ...): then a tile of the product ho
 halves of each pair, and the tensor-core kernel applies SiLU(gate) * up in its epilogue
 and writes bfloat16 directly. With few rows the product returns float32 (partial sums)
 and a small kernel adds them and applies the activation.
+
+"polynorm_mlp": u = y Wu^T, z = a N(u) + b N(u^2) + c N(u^3) + e, out = z Wd^T, where powers are
+taken element by element, N divides a token's vector by its root mean square
+(sqrt(mean(v^2) + eps)), and (a, b, c, e) are the four values of the tensor `<prefix>.act`.
+The activation is one float32 kernel over the product's partial sums.
 """
 from __future__ import annotations
 
@@ -52,4 +57,28 @@ class SwiGLU:
                 return self.down(z, split_ok=True, add_to=residual)
         gu = self.gate_up(y, split_ok=True)        # float32 [N, 2I], possibly S partials
         z = K.silu_mul(gu, self.runtime.dtype, interleaved=self.interleaved)
+        return self.down(z, split_ok=True)
+
+
+@register_part("ffn", "polynorm_mlp")
+class PolyNormMLP:
+    graph_safe = True
+
+    @classmethod
+    def tensors(cls, spec):
+        H = int(need(spec.params, "hidden_size", "polynorm_mlp"))
+        I = int(need(spec.params, "intermediate_size", "polynorm_mlp"))
+        return {f"{spec.prefix}.up": ((I, H), "matrix"), f"{spec.prefix}.down": ((H, I), "matrix"),
+                f"{spec.prefix}.act": ((4,), "norm")}
+
+    def __init__(self, spec, weights, runtime):
+        self.runtime = runtime
+        self.eps = float(need(spec.params, "eps", "polynorm_mlp"))
+        self.up = Linear(weights[f"{spec.prefix}.up"], runtime)
+        self.down = Linear(weights[f"{spec.prefix}.down"], runtime)
+        self.act = weights[f"{spec.prefix}.act"].to(device=runtime.device, dtype=torch.float32).contiguous()
+
+    def forward(self, y, ctx):
+        u = self.up(y, split_ok=True)                       # float32 [N, I], possibly S partials
+        z = K.polynorm(u, self.act, self.eps, self.runtime.dtype)
         return self.down(z, split_ok=True)

@@ -11,22 +11,36 @@ from __future__ import annotations
 import torch
 
 from ..ops import kernels as K
-from .base import need, register_part
+from .base import need, register_part, tensor_name
+
+
+class NormedUpdate:
+    """An update of the residual stream that is RMS-normed BEFORE it is added (a norm at a
+    sublayer's output): h += rmsnorm(sum of `delta`'s partial sums + `bias`) * `weight`. A block
+    hands it on as `pending` like a plain stack of partial sums, and the norm that follows does
+    the whole chain, norm of the update, add, its own norm, in one kernel."""
+    __slots__ = ("delta", "weight", "eps", "bias")
+
+    def __init__(self, delta, weight, eps, bias=None):
+        self.delta, self.weight, self.eps, self.bias = delta, weight, float(eps), bias
 
 
 @register_part("norm", "rmsnorm")
 class RMSNorm:
     @classmethod
     def tensors(cls, spec):
-        return {f"{spec.prefix}.weight": ((need(spec.params, "size", "rmsnorm"),), "norm")}
+        return {tensor_name(spec): ((need(spec.params, "size", "rmsnorm"),), "norm")}
 
     def __init__(self, spec, weights, runtime):
         p = spec.params
         self.size = int(need(p, "size", "rmsnorm"))
         self.eps = float(need(p, "eps", "rmsnorm"))
-        w = weights[f"{spec.prefix}.weight"].to(device=runtime.device, dtype=torch.float32)
+        w = weights[tensor_name(spec)].to(device=runtime.device, dtype=torch.float32)
         off = float(p.get("weight_offset", 0.0))
         self.weight = (w + off).contiguous() if off else w.contiguous()
 
     def forward(self, h, delta, out_dtype, rows=None, write_h=True):
+        if isinstance(delta, NormedUpdate):
+            return K.postnorm_add_rmsnorm(h, delta.delta, delta.bias, delta.weight, delta.eps, self.weight,
+                                          self.eps, out_dtype, rows=rows, write_h=write_h)
         return K.add_rmsnorm(h, delta, self.weight, self.eps, out_dtype, rows=rows, write_h=write_h)
