@@ -152,9 +152,10 @@ class StateStore:
         """shapes: {entry: (shape, dtype)} for a mixer's state, or {(entry, name): (shape, dtype)}
         where an entry has several (a block's own state beside its mixer's)."""
         self.pad_row = max_slots
-        self.tensors: Dict[Tuple[int, str], torch.Tensor] = {}
+        self.tensors: Dict[object, torch.Tensor] = {}
         for key, (shape, dtype) in shapes.items():
-            key = key if isinstance(key, tuple) else (key, "mixer")
+            if isinstance(key, tuple) and key[1] == "mixer":
+                key = key[0]
             self.tensors[key] = torch.zeros((max_slots + 1, *shape), dtype=dtype, device=device)
 
     def zero_slot(self, slot: int) -> None:
@@ -162,7 +163,7 @@ class StateStore:
             t[slot].zero_()
 
     def of(self, entry: int, name: str = "mixer") -> Optional[torch.Tensor]:
-        return self.tensors.get((entry, name))
+        return self.tensors.get(entry if name == "mixer" else (entry, name))
 
 
 class KVCache:

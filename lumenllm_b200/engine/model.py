@@ -64,7 +64,7 @@ class DecoderModel:
             block = self.blocks[e.layer]
             s = block.mixer.state_shape()
             if s is not None:
-                shapes[(i, "mixer")] = s
+                shapes[i] = s
             own = getattr(block, "state_shape", None)       # a block arrangement's own state
             s = own() if own else None
             if s is not None:
