@@ -200,9 +200,9 @@ def test_talking_attention_part(m, dtype):
 @pytest.mark.parametrize("decode", [False, True])
 @pytest.mark.parametrize("dtype", [F32, BF16])
 def test_one_loud_key_at_every_edge_of_sight(dtype, decode):
-    """Queries and keys are the inputs themselves (identity projections), and one earlier token is
-    made loud in a direction that the last query shares, so that this single key takes nearly all
-    of the query's weight where it is in sight and none where it is not: far back among hundreds of
+    """Queries and values are the inputs themselves and keys the inputs shifted by seven channels,
+    and one earlier token is made loud so that its KEY points where the last QUERY points (its own
+    key then points elsewhere): this single key takes nearly all of the query's weight where it is in sight and none where it is not: far back among hundreds of
     keys, on both sides of the window's edge and of the kept first tokens' edge, and on both sides
     of page borders. Beside each case stands the mask that differs by one at that edge: the plain
     result under it must be far from the right one, else the case would show nothing."""
@@ -214,6 +214,7 @@ def test_one_loud_key_at_every_edge_of_sight(dtype, decode):
         for name in ("q", "k", "v"):
             w["l0.mix." + name] = torch.eye(D).to(BF16)
             w["l0.mix." + name + ".b"] = torch.zeros(D).to(BF16)
+        w["l0.mix.k"] = torch.roll(torch.eye(D), 7, dims=0).to(BF16)
         w["l0.mix.q.norm"] = w["l0.mix.k.norm"] = torch.ones(D).to(BF16)
     mixer, w = attention_part(m, D, dtype, seed=7, edit=identity)
     g = torch.Generator().manual_seed(8)
@@ -226,13 +227,13 @@ def test_one_loud_key_at_every_edge_of_sight(dtype, decode):
              (191, None), (192, None), (255, None), (256, None), (query - 1, None)]
     for loud, off_by_one in cases:
         y = torch.randn(T, D, generator=g) * 0.3
-        y[loud] += 12 * u
+        y[loud] += 12 * torch.roll(u, -7)
         y[query] += 12 * u
         y = y.to(dtype).float()
         ref = P.talking_attention(y, w, "l0.mix.", m, 1e-6)
         if off_by_one is not None:
             wrong = P.talking_attention(y, w, "l0.mix.", off_by_one, 1e-6)
-            assert float((wrong[query] - ref[query]).abs().max()) > 100 * tol(dtype) * max(1.0, float(ref.abs().max()))
+            assert float((wrong[query] - ref[query]).abs().max()) > 10 * tol(BF16) * max(1.0, float(ref.abs().max()))
         pieces = [y[:T - 40]] + [y[t:t + 1] for t in range(T - 40, T)] if decode else [y]
         got = run_mixer(mixer, runtime(dtype), pieces)
         close(got, ref, dtype, f"loud key {loud}")
