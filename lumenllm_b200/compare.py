@@ -1,0 +1,161 @@
+"""Dabevik beside the closest other model of the library (the Qwen3 dense decoder) at equal
+sizes: prompt and decode throughput of a few layers of real-model size with random weights, and
+what each class of kernels takes of a step. `python bench.py --design dabevik` prints the result
+as one JSON line.
+
+Equal sizes: the same width, layers, vocabulary, heads, kv heads, head size, feed-forward width
+and window (every layer of the Qwen3 twin slides the same window). What differs is the design:
+two feed-forward matrices instead of three, biased projections, norms on both sides of a
+sublayer, the convolutions of the sublayers' inputs, learned positions instead of rotation, kept
+first tokens, and the mix of the heads' weights.
+"""
+from __future__ import annotations
+
+import statistics
+import time
+
+SIZES = {
+    "2k": dict(width=2048, heads=16, kv_heads=4, dim=128, ff=8192, window=1024, keep_first=4, layers=8,
+               vocab=32768, taps=4),
+    "4k": dict(width=4096, heads=32, kv_heads=8, dim=128, ff=12288, window=2048, keep_first=4, layers=4,
+               vocab=32768, taps=4),
+}
+CONTEXT = 4096
+PROMPT_TOKENS = 2048
+DECODE_PROMPTS = (1024, 2048)
+
+
+def dabevik_config(s):
+    mixer = {"heads": s["heads"], "kv_heads": s["kv_heads"], "dim": s["dim"], "vdim": s["dim"],
+             "scale": s["dim"] ** -0.5, "mask": {"size": s["window"], "keep_first": s["keep_first"]}}
+    return {"architecture": "Dabevik", "vocab": s["vocab"], "width": s["width"], "max_positions": CONTEXT,
+            "embedding": {"scale": s["width"] ** 0.5}, "norm": {"eps": 1e-6}, "canon": {"taps": s["taps"]},
+            "layers": [{"type": "attention", "mixer": mixer, "mlp": {"kind": "dense", "ff": s["ff"]}}
+                       for _ in range(s["layers"])]}
+
+
+def qwen3_config(s):
+    return dict(architectures=["Qwen3ForCausalLM"], model_type="qwen3", hidden_size=s["width"],
+                num_hidden_layers=s["layers"], num_attention_heads=s["heads"], num_key_value_heads=s["kv_heads"],
+                head_dim=s["dim"], intermediate_size=s["ff"], vocab_size=s["vocab"], rope_theta=1000000.0,
+                rms_norm_eps=1e-6, max_position_embeddings=CONTEXT, tie_word_embeddings=True,
+                sliding_window=s["window"], layer_types=["sliding_attention"] * s["layers"])
+
+
+# kernel entry point -> class of kernels, for both designs
+CLASSES = {
+    "lumen_add_rmsnorm": "norm", "lumen_postnorm_add_rmsnorm": "norm", "lumen_canon_conv": "input conv",
+    "lumen_qk_norm_rope_store": "q/k norm + cache write", "lumen_qkv_bias_norm_store": "q/k norm + cache write",
+    "lumen_rope_table": "q/k norm + cache write", "lumen_silu_mul": "activation", "lumen_polynorm": "activation",
+    "lumen_embed": "embedding", "lumen_embed_tiled": "embedding", "lumen_embed_pos": "embedding",
+    "lumen_attn_decode": "attention", "lumen_attn_decode_qkv": "attention", "lumen_attn_prefill_tc": "attention",
+    "lumen_attn_prefill": "attention", "lumen_attn_generic": "attention", "lumen_attn_talk": "attention",
+    "lumen_attn_talk_prompt": "attention", "lumen_argmax": "sampling", "lumen_sample": "sampling",
+    "lumen_gemm_tc_qkv": "qkv product + q/k norm + cache write",
+}
+
+
+def _class_times(run):
+    """Microseconds per class of kernels for one call of `run`, every launch bracketed by events."""
+    import torch
+    from .ops import native
+    rec = []
+
+    def probe(name, args):
+        label = CLASSES.get(name)
+        if label is None and name == "lumen_gemm_tc":
+            label = f"product {int(args[4])}x{int(args[5])}"
+        rec.append([label or name, torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)])
+        return rec[-1]
+    native.instrument(probe)
+    try:
+        run()
+        torch.cuda.synchronize()
+    finally:
+        native.instrument(None)
+    by = {}
+    for label, e0, e1 in rec:
+        by[label] = by.get(label, 0.0) + e0.elapsed_time(e1) * 1e3
+    return {k: round(v, 1) for k, v in sorted(by.items(), key=lambda kv: -kv[1])}, len(rec)
+
+
+def measure(config, batch, steps, warmup, seed=0):
+    """Prompt tokens/s (one prompt of PROMPT_TOKENS tokens), decode tokens/s at `batch` (captured
+    steps, tokens fed back on the device) and the classes' times of one step of each kind."""
+    import torch
+    from .engine import Engine, StepEntry
+    from .sampling import SamplingConfig
+    eng = Engine.from_random(config, seed=seed, std=0.02, dtype="bfloat16",
+                             max_tokens=batch * CONTEXT, max_slots=max(batch, 8), context_size=CONTEXT)
+    eng.graphs.min_width = CONTEXT // 64
+    g = torch.Generator().manual_seed(seed + 1)
+    prompt = torch.randint(0, eng.vocab_size, (PROMPT_TOKENS,), generator=g).tolist()
+    times = []
+    for it in range(3 + 5):
+        s = eng.alloc_slot()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        eng.step([StepEntry(s, prompt, [PROMPT_TOKENS - 1])])
+        e1.record()
+        torch.cuda.synchronize()
+        eng.free_slot(s)
+        if it >= 3:
+            times.append(e0.elapsed_time(e1))
+    prompt_ms = statistics.median(times)
+    s = eng.alloc_slot()
+    prompt_classes, prompt_launches = _class_times(lambda: eng.step([StepEntry(s, prompt, [PROMPT_TOKENS - 1])]))
+    eng.free_slot(s)
+
+    lens = torch.randint(DECODE_PROMPTS[0], DECODE_PROMPTS[1] + 1, (batch,), generator=g).tolist()
+    slots = [eng.alloc_slot() for _ in range(batch)]
+    logits = eng.step([StepEntry(sl, torch.randint(0, eng.vocab_size, (n,), generator=g).tolist(), [n - 1])
+                       for sl, n in zip(slots, lens)])
+    cfgs, us = [SamplingConfig()] * batch, [0.0] * batch
+    tok = eng.sampler.pick(logits, cfgs, us)
+    entries = [(sl, [0]) for sl in slots]
+    for _ in range(warmup):
+        tok = eng.run_device(entries, cfgs, us, tokens_on_device=tok)
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    t0 = time.perf_counter()
+    e0.record()
+    for _ in range(steps):
+        tok = eng.run_device(entries, cfgs, us, tokens_on_device=tok)
+    e1.record()
+    torch.cuda.synchronize()
+    window = (t0, time.perf_counter())
+    eng.check_kernels()
+    decode_ms = e0.elapsed_time(e1) / steps
+    per_replay = getattr(getattr(eng.graphs, "last", None), "kernels_per_replay", 0)
+    was = eng.use_graphs
+    eng.use_graphs = False
+    try:
+        for _ in range(2):
+            eng.run_device([(sl, [1]) for sl in slots], cfgs, us)
+        decode_classes, _ = _class_times(lambda: eng.run_device([(sl, [1]) for sl in slots], cfgs, us))
+    finally:
+        eng.use_graphs = was
+    for sl in slots:
+        eng.free_slot(sl)
+    return {"prompt_tokens_per_s": round(PROMPT_TOKENS / (prompt_ms * 1e-3), 1), "prompt_ms": round(prompt_ms, 3),
+            "decode_tokens_per_s": round(batch * 1000.0 / decode_ms, 1), "decode_ms_per_step": round(decode_ms, 4),
+            "decode_kernels_per_step": per_replay, "prompt_kernels": prompt_launches,
+            "prompt_us_by_class": prompt_classes, "decode_us_by_class": decode_classes, "window": window}
+
+
+def run(design, sizes, batch, steps, warmup):
+    if design != "dabevik":
+        raise ValueError(f"no comparison is written for design {design!r}")
+    import gc
+    import torch
+    out = {}
+    for name in sizes:
+        s = SIZES[name]
+        row = {"sizes": s}
+        for label, cfg in (("dabevik", dabevik_config(s)), ("qwen3", qwen3_config(s))):
+            row[label] = measure(cfg, batch, steps, warmup)
+            gc.collect()
+            torch.cuda.empty_cache()
+        out[name] = row
+    return out

@@ -20,6 +20,7 @@
 // and their order depends on the query's own position only, never on the batch. T is float
 // (32-bit path) or __nv_bfloat16; scores, weights and the mix are float32 in both.
 #include "common.cuh"
+#include "mma_utils.cuh"
 
 struct Sight {
     int lo, kept, n;
@@ -124,9 +125,18 @@ talk_scores_kernel(const T* __restrict__ q, const T* __restrict__ kcache, const 
 // there each output head's mix, written over the scores.
 #define TM_THREADS 256
 #define TM_MAX_H 128
+// With HALF the mixed weights are written as bfloat16 over the front half of each row (the
+// tensor-core values kernel reads them so): column c then lands on the bytes of the float32
+// columns c / 2, which belong to this or an earlier group of 256 columns, all read before the
+// barrier.
+// Without HALF the mix goes to a matrix of its own (Wout), and the blocks (token, group of 256
+// columns) of a token each find the heads' maxima and sums for themselves: a step of single
+// tokens has too few tokens to fill the device with a block a token.
+template <bool HALF>
 __global__ void __launch_bounds__(TM_THREADS)
-talk_softmax_mix_kernel(float* __restrict__ W, int row_stride, const int* __restrict__ tok_pos, int n0,
-                        const float* __restrict__ talk, int H, int size, int keep) {
+talk_softmax_mix_kernel(float* __restrict__ W, float* __restrict__ Wout, int row_stride,
+                        const int* __restrict__ tok_pos, int n0, const float* __restrict__ talk, int H, int size,
+                        int keep) {
     extern __shared__ __align__(16) float sm[];   // H * H (talk) + H * TM_THREADS (weights)
     __shared__ float mx[TM_MAX_H], inv[TM_MAX_H];
     float* tk = sm;
@@ -136,7 +146,9 @@ talk_softmax_mix_kernel(float* __restrict__ W, int row_stride, const int* __rest
     pdl_trigger();
     const int n = blockIdx.x;
     const Sight s = sight_of(tok_pos[n0 + n], size, keep);
+    if (!HALF && (int)blockIdx.y * TM_THREADS >= s.n) return;
     float* rows = W + (size_t)n * H * row_stride;
+    float* rows_out = Wout + (size_t)n * H * row_stride;
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     for (int g = warp; g < H; g += TM_THREADS / 32) {
         const float* row = rows + (size_t)g * row_stride;
@@ -152,19 +164,24 @@ talk_softmax_mix_kernel(float* __restrict__ W, int row_stride, const int* __rest
         }
     }
     __syncthreads();
-    for (int c0 = 0; c0 < s.n; c0 += TM_THREADS) {
+    const int c_begin = HALF ? 0 : (int)blockIdx.y * TM_THREADS, c_end = HALF ? s.n : min(s.n, c_begin + TM_THREADS);
+    for (int c0 = c_begin; c0 < c_end; c0 += TM_THREADS) {
         const int c = c0 + threadIdx.x;
         if (c < s.n)
             for (int g = 0; g < H; ++g)
                 ws[g * TM_THREADS + threadIdx.x] = expf(rows[(size_t)g * row_stride + c] - mx[g]) * inv[g];
-        // a thread reads back only what it wrote: no barrier is needed between the two halves
+        // a thread reads back only what it wrote itself; the barrier is for the narrow form,
+        // whose stores land on other threads' scores
+        if (HALF) __syncthreads();
         if (c < s.n)
             for (int h = 0; h < H; ++h) {
                 const float* t = tk + h * H;
                 float a = 0.0f;
                 for (int g = 0; g < H; ++g) a = fmaf(t[g], ws[g * TM_THREADS + threadIdx.x], a);
-                rows[(size_t)h * row_stride + c] = a;
+                if (HALF) reinterpret_cast<__nv_bfloat16*>(rows + (size_t)h * row_stride)[c] = __float2bfloat16_rn(a);
+                else rows_out[(size_t)h * row_stride + c] = a;
             }
+        if (HALF) __syncthreads();
     }
 }
 
@@ -174,7 +191,7 @@ talk_softmax_mix_kernel(float* __restrict__ W, int row_stride, const int* __rest
 // warp order. With one part the result goes out as T; with several, float32 partial results
 // [part][token][head][dv] that talk_parts_kernel adds in rising order.
 #define TV_THREADS 256
-#define TV_PART 512
+#define TV_PART 128
 template <typename T>
 __global__ void __launch_bounds__(TV_THREADS)
 talk_values_kernel(const float* __restrict__ W, int row_stride, const T* __restrict__ vcache,
@@ -188,12 +205,14 @@ talk_values_kernel(const float* __restrict__ W, int row_stride, const T* __restr
     const int g = h / (H / G);
     const Sight s = sight_of(tok_pos[n0 + n], size, keep);
     const int c_lo = z * TV_PART, c_hi = min(s.n, c_lo + TV_PART);
+    if (c_lo >= s.n) return;             // talk_parts_kernel reads only the parts a token has
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int* bt = table + (size_t)tok_seq[n0 + n] * table_stride;
     const float* row = W + ((size_t)n * H + h) * row_stride;
     float acc[8];
 #pragma unroll
     for (int k = 0; k < 8; ++k) acc[k] = 0.0f;
+#pragma unroll 4
     for (int c = c_lo + warp; c < c_hi; c += TV_THREADS / 32) {
         const int j = key_of(s, c);
         const T* tile = vcache + ((size_t)bt[j / LUMEN_PAGE] * G + g) * LUMEN_PAGE * dv;
@@ -233,12 +252,248 @@ __global__ void talk_parts_kernel(const float* __restrict__ parts, int Z, size_t
     out[(size_t)n0 * row_width + i] = from_f32<T>(a);
 }
 
+// ---------------------------------------------------------------- prompts: 1. and 3. on the tensor cores
+// For steps in which sequences bring many tokens (bfloat16, key and value sizes multiples of
+// 16, values of at most 128): a block takes 64 consecutive queries of ONE sequence and one
+// head, and walks the cache pages that any of them sees (the pages of the kept first keys,
+// then those of the window). A page is a 64-key tile; `mma.sync` m16n8k16 with float32
+// accumulators, a warp 16 queries. The scores kernel leaves scale * q . k at each visible
+// (query, key) pair's column; the values kernel reads the mixed weights (bfloat16, written
+// over the front half of each row by the mix kernel), zero where a key is out of sight, and
+// multiplies them with the page's values. Blocks find their sequence and tile from cu_q on the
+// device; blocks beyond the step's tiles leave at once. Tokens outside [n0, n0 + n_rows) (the
+// rows the scratch matrix holds in this pass) are skipped.
+#define TP_Q 64
+#define TP_THREADS 128
+
+struct PromptTile {
+    int b, tok0, rows, p0, lo_page, hi_page, kept_pages;
+};
+__device__ __forceinline__ bool prompt_tile(int tile, const int* cu_q, const int* seq_start, int B, int size,
+                                            int keep, PromptTile& t) {
+    int b = 0;
+    for (; b < B; ++b) {
+        const int nt = (cu_q[b + 1] - cu_q[b] + TP_Q - 1) / TP_Q;
+        if (tile < nt) break;
+        tile -= nt;
+    }
+    if (b == B) return false;
+    t.b = b;
+    t.tok0 = cu_q[b] + tile * TP_Q;
+    t.rows = min(TP_Q, cu_q[b + 1] - t.tok0);
+    t.p0 = seq_start[b] + tile * TP_Q;
+    const int lo = (size > 0 && t.p0 - size + 1 > 0) ? t.p0 - size + 1 : 0;   // of the tile's first query
+    t.lo_page = lo / LUMEN_PAGE;
+    t.hi_page = (t.p0 + t.rows - 1) / LUMEN_PAGE;
+    t.kept_pages = min((keep + LUMEN_PAGE - 1) / LUMEN_PAGE, t.lo_page);
+    return true;
+}
+
+// rows x width values of 2 bytes, row-major with `ld` values between rows in global memory,
+// into shared memory rows of `pitch` values; rows beyond `rows` are zeroed.
+__device__ __forceinline__ void stage_rows(__nv_bfloat16* dst, int pitch, const __nv_bfloat16* src, size_t ld,
+                                           int rows, int width) {
+    const int chunks = width / 8;
+    for (int i = threadIdx.x; i < TP_Q * chunks; i += TP_THREADS) {
+        const int r = i / chunks, c = i - r * chunks;
+        uint4 v = make_uint4(0u, 0u, 0u, 0u);
+        if (r < rows) v = *reinterpret_cast<const uint4*>(src + (size_t)r * ld + 8 * c);
+        *reinterpret_cast<uint4*>(dst + (size_t)r * pitch + 8 * c) = v;
+    }
+}
+
+__global__ void __launch_bounds__(TP_THREADS)
+talk_scores_mma_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restrict__ kcache,
+                       const int* __restrict__ table, int table_stride, const int* __restrict__ cu_q,
+                       const int* __restrict__ seq_start, int B, float* __restrict__ W, int row_stride, int n0,
+                       int n_rows, int H, int G, int d, int size, int keep, float scale) {
+    extern __shared__ __align__(16) __nv_bfloat16 sh[];     // queries [64][d + 8], keys [64][d + 8]
+    pdl_wait();
+    pdl_trigger();
+    PromptTile t;
+    if (!prompt_tile(blockIdx.x, cu_q, seq_start, B, size, keep, t)) return;
+    if (t.tok0 + t.rows <= n0 || t.tok0 >= n0 + n_rows) return;
+    const int h = blockIdx.y, g = h / (H / G), pitch = d + 8;
+    __nv_bfloat16* Qs = sh;
+    __nv_bfloat16* Ks = sh + TP_Q * pitch;
+    stage_rows(Qs, pitch, q + ((size_t)t.tok0 * H + h) * d, (size_t)H * d, t.rows, d);
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int* bt = table + (size_t)t.b * table_stride;
+    const int a_row = warp * 16 + (lane & 7) + 8 * ((lane >> 3) & 1), a_col = 8 * (lane >> 4);
+    const int b_row = (lane & 7) + 8 * (lane >> 4), b_col = 8 * ((lane >> 3) & 1);
+    const int n_pages = t.kept_pages + t.hi_page - t.lo_page + 1;
+    for (int pi = 0; pi < n_pages; ++pi) {
+        const int page_idx = pi < t.kept_pages ? pi : t.lo_page + pi - t.kept_pages;
+        __syncthreads();             // the tile before is read; the first time: nothing yet
+        stage_rows(Ks, pitch, kcache + ((size_t)bt[page_idx] * G + g) * LUMEN_PAGE * d, (size_t)d, LUMEN_PAGE, d);
+        __syncthreads();
+        float acc[8][4];
+#pragma unroll
+        for (int nt = 0; nt < 8; ++nt)
+#pragma unroll
+            for (int k = 0; k < 4; ++k) acc[nt][k] = 0.0f;
+        for (int ks = 0; ks < d / 16; ++ks) {
+            uint32_t a[4];
+            ldsm_x4(a, smem_u32(Qs + (size_t)a_row * pitch + 16 * ks + a_col));
+#pragma unroll
+            for (int np = 0; np < 4; ++np) {
+                uint32_t bf[4];
+                ldsm_x4(bf, smem_u32(Ks + (size_t)(16 * np + b_row) * pitch + 16 * ks + b_col));
+                mma_bf16(acc[2 * np], a, bf[0], bf[1]);
+                mma_bf16(acc[2 * np + 1], a, bf[2], bf[3]);
+            }
+        }
+#pragma unroll
+        for (int half = 0; half < 2; ++half) {
+            const int i = warp * 16 + (lane >> 2) + 8 * half;
+            const int tok = t.tok0 + i;
+            if (i >= t.rows || tok < n0 || tok >= n0 + n_rows) continue;
+            const Sight s = sight_of(t.p0 + i, size, keep);
+            float* row = W + ((size_t)(tok - n0) * H + h) * row_stride;
+#pragma unroll
+            for (int nt = 0; nt < 8; ++nt)
+#pragma unroll
+                for (int k = 0; k < 2; ++k) {
+                    const int j = page_idx * LUMEN_PAGE + nt * 8 + 2 * (lane & 3) + k;
+                    if (j > t.p0 + i || (j < s.lo && j >= s.kept)) continue;
+                    row[j < s.kept ? j : s.kept + (j - s.lo)] = acc[nt][2 * half + k] * scale;
+                }
+        }
+    }
+}
+
+template <int NT>      // value size / 8
+__global__ void __launch_bounds__(TP_THREADS)
+talk_values_mma_kernel(const float* __restrict__ W, int row_stride, const __nv_bfloat16* __restrict__ vcache,
+                       const int* __restrict__ table, int table_stride, const int* __restrict__ cu_q,
+                       const int* __restrict__ seq_start, int B, __nv_bfloat16* __restrict__ out, int n0, int n_rows,
+                       int H, int G, int size, int keep) {
+    constexpr int dv = NT * 8, vpitch = dv + 8, ppitch = LUMEN_PAGE + 8;
+    __shared__ __align__(16) __nv_bfloat16 Ps[TP_Q * ppitch];
+    __shared__ __align__(16) __nv_bfloat16 Vs[LUMEN_PAGE * vpitch];
+    pdl_wait();
+    pdl_trigger();
+    PromptTile t;
+    if (!prompt_tile(blockIdx.x, cu_q, seq_start, B, size, keep, t)) return;
+    if (t.tok0 + t.rows <= n0 || t.tok0 >= n0 + n_rows) return;
+    const int h = blockIdx.y, g = h / (H / G);
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int* bt = table + (size_t)t.b * table_stride;
+    const int a_row = warp * 16 + (lane & 7) + 8 * ((lane >> 3) & 1), a_col = 8 * (lane >> 4);
+    const int v_row = (lane & 7) + 8 * ((lane >> 3) & 1), v_col = 8 * (lane >> 4);
+    float acc[NT][4];
+#pragma unroll
+    for (int nt = 0; nt < NT; ++nt)
+#pragma unroll
+        for (int k = 0; k < 4; ++k) acc[nt][k] = 0.0f;
+    const int n_pages = t.kept_pages + t.hi_page - t.lo_page + 1;
+    for (int pi = 0; pi < n_pages; ++pi) {
+        const int page_idx = pi < t.kept_pages ? pi : t.lo_page + pi - t.kept_pages;
+        __syncthreads();
+        // the page's weights for the tile's queries: two threads a query, 32 keys each
+        {
+            const int i = threadIdx.x >> 1, j0 = page_idx * LUMEN_PAGE + 32 * (threadIdx.x & 1);
+            const int tok = t.tok0 + i;
+            const bool live = i < t.rows && tok >= n0 && tok < n0 + n_rows;
+            const Sight s = sight_of(t.p0 + (live ? i : 0), size, keep);
+            const __nv_bfloat16* row =
+                reinterpret_cast<const __nv_bfloat16*>(W + ((size_t)(live ? tok - n0 : 0) * H + h) * row_stride);
+            __nv_bfloat16* dst = Ps + (size_t)i * ppitch + 32 * (threadIdx.x & 1);
+            for (int k = 0; k < 32; ++k) {
+                const int j = j0 + k;
+                const bool seen = live && j <= t.p0 + i && (j >= s.lo || j < s.kept);
+                dst[k] = seen ? row[j < s.kept ? j : s.kept + (j - s.lo)] : __float2bfloat16_rn(0.0f);
+            }
+        }
+        stage_rows(Vs, vpitch, vcache + ((size_t)bt[page_idx] * G + g) * LUMEN_PAGE * dv, (size_t)dv, LUMEN_PAGE, dv);
+        __syncthreads();
+#pragma unroll
+        for (int ks = 0; ks < LUMEN_PAGE / 16; ++ks) {
+            uint32_t a[4];
+            ldsm_x4(a, smem_u32(Ps + (size_t)a_row * ppitch + 16 * ks + a_col));
+#pragma unroll
+            for (int np = 0; np < NT / 2; ++np) {
+                uint32_t bf[4];
+                ldsm_x4_t(bf, smem_u32(Vs + (size_t)(16 * ks + v_row) * vpitch + 16 * np + v_col));
+                mma_bf16(acc[2 * np], a, bf[0], bf[1]);
+                mma_bf16(acc[2 * np + 1], a, bf[2], bf[3]);
+            }
+        }
+    }
+#pragma unroll
+    for (int half = 0; half < 2; ++half) {
+        const int i = warp * 16 + (lane >> 2) + 8 * half;
+        const int tok = t.tok0 + i;
+        if (i >= t.rows || tok < n0 || tok >= n0 + n_rows) continue;
+        __nv_bfloat16* orow = out + ((size_t)tok * H + h) * dv;
+#pragma unroll
+        for (int nt = 0; nt < NT; ++nt)
+            *reinterpret_cast<uint32_t*>(orow + nt * 8 + 2 * (lane & 3)) = pack_bf16(acc[nt][2 * half], acc[nt][2 * half + 1]);
+    }
+}
+
+template <int NT>
+static void launch_values_mma(dim3 grid, cudaStream_t stream, const float* W, int row_stride, const __nv_bfloat16* vc,
+                              const int* table, int table_stride, const int* cu_q, const int* seq_start, int B,
+                              __nv_bfloat16* out, int n0, int n_rows, int H, int G, int size, int keep) {
+    lumen_launch(talk_values_mma_kernel<NT>, grid, dim3(TP_THREADS), 0, stream, W, row_stride, vc, table, table_stride,
+                 cu_q, seq_start, B, out, n0, n_rows, H, G, size, keep);
+}
+
+LUMEN_API int lumen_attn_talk_prompt_ok(int H, int G, int d, int dv) {
+    return H > 0 && G > 0 && H % G == 0 && H <= TM_MAX_H && d % 16 == 0 && d >= 16 && d <= 256 && dv % 16 == 0 &&
+           dv >= 16 && dv <= 128;
+}
+
+// The three kernels for a step of prompts. n_tiles bounds the number of (sequence, 64-query)
+// tiles (N / 64 + B does for any division of N tokens into B sequences).
+LUMEN_API int lumen_attn_talk_prompt(const void* q, const void* kc, const void* vc, const int* table, int table_stride,
+                                     const int* cu_q, const int* seq_start, int B, int n_tiles, const int* tok_pos,
+                                     const float* talk, void* out, float* W, int N, int rows_per_pass, int row_stride,
+                                     int H, int G, int d, int dv, int size, int keep, float scale,
+                                     cudaStream_t stream) {
+    if (N <= 0) return 0;
+    if (!lumen_attn_talk_prompt_ok(H, G, d, dv) || B <= 0 || n_tiles <= 0 || rows_per_pass <= 0 || row_stride <= 0 ||
+        size < 0 || keep < 0 || H > 65535)
+        return LUMEN_ERR_UNSUPPORTED;
+    const size_t smem1 = (size_t)2 * TP_Q * (d + 8) * sizeof(__nv_bfloat16);
+    const size_t smem2 = ((size_t)H * H + (size_t)H * TM_THREADS) * sizeof(float);
+    if (smem2 > 200 * 1024) return LUMEN_ERR_UNSUPPORTED;
+    if (smem1 > 48 * 1024)
+        cudaFuncSetAttribute(talk_scores_mma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem1);
+    if (smem2 > 48 * 1024)
+        cudaFuncSetAttribute(talk_softmax_mix_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem2);
+    const dim3 grid(n_tiles, H);
+    for (int n0 = 0; n0 < N; n0 += rows_per_pass) {
+        const int rows = min(rows_per_pass, N - n0);
+        lumen_launch(talk_scores_mma_kernel, grid, dim3(TP_THREADS), smem1, stream, (const __nv_bfloat16*)q,
+                     (const __nv_bfloat16*)kc, table, table_stride, cu_q, seq_start, B, W, row_stride, n0, rows, H, G, d,
+                     size, keep, scale);
+        lumen_launch(talk_softmax_mix_kernel<true>, dim3(rows), dim3(TM_THREADS), smem2, stream, W, W, row_stride,
+                     tok_pos, n0, talk, H, size, keep);
+#define LUMEN_TALK_VALUES(NT_)                                                                                        \
+    case NT_:                                                                                                         \
+        launch_values_mma<NT_>(grid, stream, (const float*)W, row_stride, (const __nv_bfloat16*)vc, table,            \
+                               table_stride, cu_q, seq_start, B, (__nv_bfloat16*)out, n0, rows, H, G, size, keep);    \
+        break;
+        switch (dv / 8) {
+            LUMEN_TALK_VALUES(2) LUMEN_TALK_VALUES(4) LUMEN_TALK_VALUES(6) LUMEN_TALK_VALUES(8) LUMEN_TALK_VALUES(10)
+            LUMEN_TALK_VALUES(12) LUMEN_TALK_VALUES(14) LUMEN_TALK_VALUES(16)
+            default: return LUMEN_ERR_UNSUPPORTED;
+        }
+#undef LUMEN_TALK_VALUES
+        cudaError_t e = cudaGetLastError();
+        if (e != cudaSuccess) return (int)e;
+    }
+    return 0;
+}
+
 // ---------------------------------------------------------------- host side
-// q [N, H, d], out [N, H, dv]; scratch: float32 [rows, H, row_stride] with rows >= min(N,
-// rows_per_pass); parts: float32 [Z, rows, H, dv] when row_stride > TV_PART (Z parts), else null.
+// q [N, H, d], out [N, H, dv]; scratch: W (scores) and W2 (mixed weights), each float32
+// [rows, H, row_stride] with rows >= min(N, rows_per_pass); parts: float32 [Z, rows, H, dv] when row_stride > TV_PART (Z parts), else null.
 template <typename T>
 static int attn_talk_run(const T* q, const T* kc, const T* vc, const int* table, int table_stride, const int* tok_seq,
-                         const int* tok_pos, const float* talk, T* out, float* W, float* parts, int N,
+                         const int* tok_pos, const float* talk, T* out, float* W, float* W2, float* parts, int N,
                          int rows_per_pass, int row_stride, int H, int G, int d, int dv, int size, int keep,
                          float scale, int k_layout, int v_layout, cudaStream_t stream) {
     const int per = H / G;
@@ -250,14 +505,14 @@ static int attn_talk_run(const T* q, const T* kc, const T* vc, const int* table,
     if (smem1 > 48 * 1024)
         cudaFuncSetAttribute(talk_scores_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem1);
     if (smem2 > 48 * 1024)
-        cudaFuncSetAttribute(talk_softmax_mix_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem2);
+        cudaFuncSetAttribute(talk_softmax_mix_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem2);
     for (int n0 = 0; n0 < N; n0 += rows_per_pass) {
         const int rows = min(rows_per_pass, N - n0);
         lumen_launch(talk_scores_kernel<T>, dim3(rows, G, chunks), dim3(TS_THREADS), smem1, stream, q, kc, table,
                      table_stride, tok_seq, tok_pos, W, row_stride, n0, H, G, d, size, keep, scale, k_layout);
-        lumen_launch(talk_softmax_mix_kernel, dim3(rows), dim3(TM_THREADS), smem2, stream, W, row_stride, tok_pos, n0,
-                     talk, H, size, keep);
-        lumen_launch(talk_values_kernel<T>, dim3(rows, H, Z), dim3(TV_THREADS), 0, stream, (const float*)W, row_stride,
+        lumen_launch(talk_softmax_mix_kernel<false>, dim3(rows, (row_stride + TM_THREADS - 1) / TM_THREADS),
+                     dim3(TM_THREADS), smem2, stream, W, W2, row_stride, tok_pos, n0, talk, H, size, keep);
+        lumen_launch(talk_values_kernel<T>, dim3(rows, H, Z), dim3(TV_THREADS), 0, stream, (const float*)W2, row_stride,
                      vc, table, table_stride, tok_seq, tok_pos, out, Z > 1 ? parts : (float*)nullptr, n0, rows, H, G, dv,
                      size, keep, v_layout);
         if (Z > 1) {
@@ -273,7 +528,7 @@ static int attn_talk_run(const T* q, const T* kc, const T* vc, const int* table,
 
 LUMEN_API int lumen_attn_talk(const void* q, const void* kc, const void* vc, const int* table, int table_stride,
                               const int* tok_seq, const int* tok_pos, const float* talk, void* out, float* W,
-                              float* parts, int is_bf16, int N, int rows_per_pass, int row_stride, int H, int G, int d,
+                              float* W2, float* parts, int is_bf16, int N, int rows_per_pass, int row_stride, int H, int G, int d,
                               int dv, int size, int keep, float scale, int k_layout, int v_layout,
                               cudaStream_t stream) {
     if (N <= 0) return 0;
@@ -283,13 +538,13 @@ LUMEN_API int lumen_attn_talk(const void* q, const void* kc, const void* vc, con
     if ((row_stride + TS_COLS - 1) / TS_COLS > 65535) return LUMEN_ERR_UNSUPPORTED;
     if ((k_layout == LUMEN_LAYOUT_SW128 && (!is_bf16 || d % 64)) || (v_layout == LUMEN_LAYOUT_SW128 && (!is_bf16 || dv % 64)))
         return LUMEN_ERR_UNSUPPORTED;
-    if (row_stride > TV_PART && !parts) return LUMEN_ERR_BAD_ARGUMENT;
+    if ((row_stride > TV_PART && !parts) || !W || !W2 || W == W2) return LUMEN_ERR_BAD_ARGUMENT;
     if (is_bf16)
         return attn_talk_run<__nv_bfloat16>((const __nv_bfloat16*)q, (const __nv_bfloat16*)kc, (const __nv_bfloat16*)vc,
-                                            table, table_stride, tok_seq, tok_pos, talk, (__nv_bfloat16*)out, W, parts, N,
+                                            table, table_stride, tok_seq, tok_pos, talk, (__nv_bfloat16*)out, W, W2, parts, N,
                                             rows_per_pass, row_stride, H, G, d, dv, size, keep, scale, k_layout,
                                             v_layout, stream);
     return attn_talk_run<float>((const float*)q, (const float*)kc, (const float*)vc, table, table_stride, tok_seq,
-                                tok_pos, talk, (float*)out, W, parts, N, rows_per_pass, row_stride, H, G, d, dv, size,
+                                tok_pos, talk, (float*)out, W, W2, parts, N, rows_per_pass, row_stride, H, G, d, dv, size,
                                 keep, scale, k_layout, v_layout, stream);
 }

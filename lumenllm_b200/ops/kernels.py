@@ -197,15 +197,27 @@ def qkv_bias_norm_store(qkv, bias, q_norm_w, k_norm_w, eps, cache_pos, tok_seq, 
 
 
 ATTN_TALK_SCRATCH_BYTES = 256 << 20     # weights matrix of one pass over a step's tokens
-ATTN_TALK_PART = 512                    # columns a block of the values kernel walks (TV_PART)
+ATTN_TALK_PART = 128                    # columns a block of the values kernel walks (TV_PART)
+
+
+ATTN_TALK_PROMPT_SCRATCH_BYTES = 1 << 30
+
+
+def attn_talk_prompt_takes(q, nkv, dv, k_layout, v_layout) -> bool:
+    """Whether the tensor-core kernels take this step (bfloat16, plain tiles, sizes in 16s)."""
+    return (q.dtype == BF16 and k_layout == LAYOUT_LINEAR and v_layout == LAYOUT_LINEAR and
+            bool(int_fn("attn_talk", "lumen_attn_talk_prompt_ok", [c_int] * 4)(
+                int(q.shape[1]), int(nkv), int(q.shape[2]), int(dv))))
 
 
 def attn_talk(q, kcache, vcache, block_table, tok_seq, tok_pos, talk, window, keep_first, scale, dv,
-              k_layout=LAYOUT_LINEAR, v_layout=LAYOUT_LINEAR, prompt=False):
+              k_layout=LAYOUT_LINEAR, v_layout=LAYOUT_LINEAR, cu_q=None, seq_start=None, n_seqs=0):
     """Attention with softmax weights mixed across heads (talk float32 [nq, nq]) before they meet
     the values, over the paged cache; a query at position p sees key j <= p if p - j < window
     (window 0: every key) or j < keep_first. q [N, nq, d]; keys [pages, nkv, PAGE, d]; values
-    [pages, nkv, PAGE, dv]; returns [N, nq, dv] in q's type."""
+    [pages, nkv, PAGE, dv]; returns [N, nq, dv] in q's type. With cu_q int32 [B + 1], seq_start
+    int32 [B] and n_seqs = B (a step of prompts) the scores and the value products run on the
+    tensor cores where attn_talk_prompt_takes says so."""
     N, nq, d = q.shape
     nkv = kcache.shape[1]
     require(q, q.dtype, "attn_talk.q")
@@ -220,16 +232,32 @@ def attn_talk(q, kcache, vcache, block_table, tok_seq, tok_pos, talk, window, ke
                           f"{tuple(vcache.shape)} do not fit {nq} heads of {d} / {dv}")
     bound = block_table.shape[1] * PAGE           # no sequence of the step is longer than its page table
     row_stride = max(1, min(int(window) + int(keep_first), bound) if window > 0 else bound)
-    rows_per_pass = max(1, min(N, ATTN_TALK_SCRATCH_BYTES // (nq * row_stride * 4)))
     out = torch.empty((N, nq, dv), dtype=q.dtype, device=q.device)
-    W = torch.empty((rows_per_pass, nq, row_stride), dtype=F32, device=q.device)
+    if cu_q is not None and n_seqs > 0 and attn_talk_prompt_takes(q, nkv, dv, k_layout, v_layout):
+        require(cu_q, I32, "attn_talk.cu_q")
+        require(seq_start, I32, "attn_talk.seq_start")
+        if cu_q.numel() < n_seqs + 1 or seq_start.numel() < n_seqs:
+            raise KernelError("attn_talk: metadata shorter than the batch")
+        row_stride = (row_stride + 3) // 4 * 4
+        rows_per_pass = max(1, min(N, ATTN_TALK_PROMPT_SCRATCH_BYTES // (nq * row_stride * 4)))
+        W = torch.empty((rows_per_pass, nq, row_stride), dtype=F32, device=q.device)
+        f = fn("attn_talk", "lumen_attn_talk_prompt",
+               [P, P, P, P, c_int, P, P, c_int, c_int, P, P, P, P, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
+                c_int, c_int, c_float, P])
+        check(f(ptr(q), ptr(kcache), ptr(vcache), ptr(block_table), block_table.stride(0), ptr(cu_q), ptr(seq_start),
+                int(n_seqs), N // 64 + int(n_seqs), ptr(tok_pos), ptr(talk), ptr(out), ptr(W), N, rows_per_pass,
+                row_stride, nq, nkv, d, dv, int(window), int(keep_first), float(scale), stream_ptr()),
+              "attn_talk_prompt")
+        return out
+    rows_per_pass = max(1, min(N, ATTN_TALK_SCRATCH_BYTES // (2 * nq * row_stride * 4)))
+    W = torch.empty((2, rows_per_pass, nq, row_stride), dtype=F32, device=q.device)   # scores, mixed weights
     Z = -(-row_stride // ATTN_TALK_PART)
     parts = torch.empty((Z, rows_per_pass, nq, dv), dtype=F32, device=q.device) if Z > 1 else None
     f = fn("attn_talk", "lumen_attn_talk",
-           [P, P, P, P, c_int, P, P, P, P, P, P, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
+           [P, P, P, P, c_int, P, P, P, P, P, P, P, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
             c_float, c_int, c_int, P])
     check(f(ptr(q), ptr(kcache), ptr(vcache), ptr(block_table), block_table.stride(0), ptr(tok_seq), ptr(tok_pos),
-            ptr(talk), ptr(out), ptr(W), ptr(parts), _is_bf16(q), N, rows_per_pass, row_stride, nq, nkv, d, dv,
+            ptr(talk), ptr(out), ptr(W[0]), ptr(W[1]), ptr(parts), _is_bf16(q), N, rows_per_pass, row_stride, nq, nkv, d, dv,
             int(window), int(keep_first), float(scale), int(k_layout), int(v_layout), stream_ptr()), "attn_talk")
     return out
 

@@ -73,8 +73,11 @@ class TalkingAttention:
         q = K.qkv_bias_norm_store(qkv, self.qkv_bias, self.q_norm, self.k_norm, self.eps, ctx.cache_pos,
                                   ctx.tok_seq, table, kc, vc, self.H, self.G, self.d, self.dv,
                                   self.runtime.dtype)
+        # steps in which sequences bring many tokens go to the tensor cores; one token each, to
+        # the kernels that spread a sequence's keys over the device
+        prompt = {} if ctx.is_decode else dict(cu_q=ctx.cu_q, seq_start=ctx.seq_start, n_seqs=ctx.B)
         out = K.attn_talk(q, kc, vc, table, ctx.tok_seq, ctx.cache_pos, self.talk, self.window,
-                          self.keep_first, self.scale, self.dv, prompt=not ctx.is_decode)
+                          self.keep_first, self.scale, self.dv, **prompt)
         delta = self.o(out.view(-1, self.H * self.dv), split_ok=True)
         if not bias_downstream:
             (delta[0] if delta.dim() == 3 else delta).add_(self.update_bias)
