@@ -390,20 +390,23 @@ talk_values_mma_kernel(const float* __restrict__ W, int row_stride, const __nv_b
     for (int pi = 0; pi < n_pages; ++pi) {
         const int page_idx = pi < t.kept_pages ? pi : t.lo_page + pi - t.kept_pages;
         __syncthreads();
-        // the page's weights for the tile's queries: two threads a query, 32 keys each
-        {
-            const int i = threadIdx.x >> 1, j0 = page_idx * LUMEN_PAGE + 32 * (threadIdx.x & 1);
-            const int tok = t.tok0 + i;
+        // the page's weights for the tile's queries: a warp takes its 16 queries one after the
+        // other, a lane two neighbouring keys, so a query's 64 weights are one 128-byte read
+#pragma unroll 4
+        for (int rr = 0; rr < 16; ++rr) {
+            const int i = warp * 16 + rr, tok = t.tok0 + i;
             const bool live = i < t.rows && tok >= n0 && tok < n0 + n_rows;
             const Sight s = sight_of(t.p0 + (live ? i : 0), size, keep);
             const __nv_bfloat16* row =
                 reinterpret_cast<const __nv_bfloat16*>(W + ((size_t)(live ? tok - n0 : 0) * H + h) * row_stride);
-            __nv_bfloat16* dst = Ps + (size_t)i * ppitch + 32 * (threadIdx.x & 1);
-            for (int k = 0; k < 32; ++k) {
-                const int j = j0 + k;
+            float w2[2];
+#pragma unroll
+            for (int k = 0; k < 2; ++k) {
+                const int j = page_idx * LUMEN_PAGE + 2 * lane + k;
                 const bool seen = live && j <= t.p0 + i && (j >= s.lo || j < s.kept);
-                dst[k] = seen ? row[j < s.kept ? j : s.kept + (j - s.lo)] : __float2bfloat16_rn(0.0f);
+                w2[k] = seen ? __bfloat162float(row[j < s.kept ? j : s.kept + (j - s.lo)]) : 0.0f;
             }
+            *reinterpret_cast<uint32_t*>(Ps + (size_t)i * ppitch + 2 * lane) = pack_bf16(w2[0], w2[1]);
         }
         stage_rows(Vs, vpitch, vcache + ((size_t)bt[page_idx] * G + g) * LUMEN_PAGE * dv, (size_t)dv, LUMEN_PAGE, dv);
         __syncthreads();

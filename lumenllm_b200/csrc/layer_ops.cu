@@ -14,6 +14,34 @@
 __device__ __forceinline__ float ld_f32(const float* p) { return *p; }
 __device__ __forceinline__ float ld_f32(const __nv_bfloat16* p) { return __bfloat162float(*p); }
 
+// V consecutive values at a time: 4 where a row's width is a multiple of 4 (16-byte moves), else 1.
+template <int V> struct Vals { float v[V]; };
+template <int V> __device__ __forceinline__ Vals<V> ldv(const float* p) {
+    Vals<V> r;
+    if (V == 4) {
+        const float4 t = *reinterpret_cast<const float4*>(p);
+        r.v[0] = t.x; r.v[1 % V] = t.y; r.v[2 % V] = t.z; r.v[3 % V] = t.w;
+    } else {
+        r.v[0] = *p;
+    }
+    return r;
+}
+template <int V> __device__ __forceinline__ void stv(float* p, const Vals<V>& x) {
+    if (V == 4) *reinterpret_cast<float4*>(p) = make_float4(x.v[0], x.v[1 % V], x.v[2 % V], x.v[3 % V]);
+    else *p = x.v[0];
+}
+template <int V> __device__ __forceinline__ void stv(__nv_bfloat16* p, const Vals<V>& x) {
+    if (V == 4) {
+        __nv_bfloat162 lo = __floats2bfloat162_rn(x.v[0], x.v[1 % V]), hi = __floats2bfloat162_rn(x.v[2 % V], x.v[3 % V]);
+        uint2 u;
+        u.x = *reinterpret_cast<uint32_t*>(&lo);
+        u.y = *reinterpret_cast<uint32_t*>(&hi);
+        *reinterpret_cast<uint2*>(p) = u;
+    } else {
+        *p = __float2bfloat16_rn(x.v[0]);
+    }
+}
+
 // ---------------------------------------------------------------- embedding + position
 // h[t, :] = float(E[token[t], :]) * scale + float(P[pos[t], :]). A token or a position outside
 // its table contributes zeros (the host has refused it before; this is the second guard).
@@ -106,12 +134,17 @@ LUMEN_API int lumen_embed_pos(const int* tokens, const void* table, int table_is
 // u = delta[0][r] + ... + delta[S-1][r] (+ bias);  x = h[r] + u / sqrt(mean(u^2) + eps_u) * wu;
 // if write_h, h[r] = x;  if wn, y[b] = x / sqrt(mean(x^2) + eps_n) * wn.
 // With `rows`, block b reads row rows[b] and writes y row b; without, row b.
-template <typename TOut>
+// With `cw` (a step in which row b is the ONE new token of sequence b): what goes out is the
+// convolution of the sublayer's input, y + sum_j cw[j] * (the sequence's last inputs, then y),
+// and the sequence's state (row seq_slot[b] of `state`) moves on by y; see canon_conv_kernel.
+#define CANON_MAX_TAPS 16
+template <typename TOut, int V>
 __global__ void __launch_bounds__(1024)
 postnorm_add_rmsnorm_kernel(float* __restrict__ h, const float* __restrict__ delta, int S, size_t delta_stride,
                             const float* __restrict__ bias, const float* __restrict__ wu, float eps_u,
                             const float* __restrict__ wn, float eps_n, TOut* __restrict__ y,
-                            const int* __restrict__ rows, int H, int write_h) {
+                            const int* __restrict__ rows, int H, int write_h, const float* __restrict__ cw, int taps,
+                            float* __restrict__ state, size_t slot_stride, const int* __restrict__ seq_slot) {
     extern __shared__ __align__(16) float xs[];  // H floats
     __shared__ float red[32];
     pdl_trigger();
@@ -119,29 +152,67 @@ postnorm_add_rmsnorm_kernel(float* __restrict__ h, const float* __restrict__ del
     const int b = blockIdx.x;
     const int r = rows ? rows[b] : b;
     float* hr = h + (size_t)r * H;
-    const float* dr = delta + (size_t)r * H;
     float ss = 0.0f;
-    for (int i = threadIdx.x; i < H; i += blockDim.x) {
-        float u = dr[i];
-        for (int s = 1; s < S; ++s) u += dr[(size_t)s * delta_stride + i];
-        if (bias) u += bias[i];
-        xs[i] = u;
-        ss += u * u;
+    if (delta) {
+        const float* dr = delta + (size_t)r * H;
+        for (int i = threadIdx.x * V; i < H; i += blockDim.x * V) {
+            Vals<V> u = ldv<V>(dr + i);
+            for (int s = 1; s < S; ++s) {
+                const Vals<V> d = ldv<V>(dr + (size_t)s * delta_stride + i);
+#pragma unroll
+                for (int k = 0; k < V; ++k) u.v[k] += d.v[k];
+            }
+            if (bias) {
+                const Vals<V> d = ldv<V>(bias + i);
+#pragma unroll
+                for (int k = 0; k < V; ++k) u.v[k] += d.v[k];
+            }
+            stv<V>(xs + i, u);
+#pragma unroll
+            for (int k = 0; k < V; ++k) ss += u.v[k] * u.v[k];
+        }
+        ss = block_sum(ss, red);
     }
-    ss = block_sum(ss, red);
     const float su = 1.0f / sqrtf(ss / (float)H + eps_u);
     float ss2 = 0.0f;
-    for (int i = threadIdx.x; i < H; i += blockDim.x) {
-        const float x = hr[i] + xs[i] * su * wu[i];
-        xs[i] = x;
-        if (write_h) hr[i] = x;
-        ss2 += x * x;
+    for (int i = threadIdx.x * V; i < H; i += blockDim.x * V) {
+        Vals<V> x = ldv<V>(hr + i);
+        if (delta) {
+            const Vals<V> u = ldv<V>(xs + i), g = ldv<V>(wu + i);
+#pragma unroll
+            for (int k = 0; k < V; ++k) x.v[k] += u.v[k] * su * g.v[k];
+            if (write_h) stv<V>(hr + i, x);
+        }
+        stv<V>(xs + i, x);
+#pragma unroll
+        for (int k = 0; k < V; ++k) ss2 += x.v[k] * x.v[k];
     }
     if (wn == nullptr) return;
     ss2 = block_sum(ss2, red);
     const float sn = 1.0f / sqrtf(ss2 / (float)H + eps_n);
     TOut* yr = y + (size_t)b * H;
-    for (int i = threadIdx.x; i < H; i += blockDim.x) yr[i] = from_f32<TOut>(xs[i] * sn * wn[i]);
+    float* st = cw && taps > 1 ? state + (size_t)seq_slot[b] * slot_stride : nullptr;
+    const int back = taps - 1;
+    for (int i = threadIdx.x * V; i < H; i += blockDim.x * V) {
+        const Vals<V> x = ldv<V>(xs + i), g = ldv<V>(wn + i);
+        Vals<V> o;
+#pragma unroll
+        for (int k = 0; k < V; ++k) o.v[k] = x.v[k] * sn * g.v[k];
+        if (cw) {
+            const Vals<V> cur = o;
+            for (int j = 0; j < back; ++j) {
+                const Vals<V> w = ldv<V>(cw + (size_t)j * H + i), old = ldv<V>(st + (size_t)j * H + i);
+#pragma unroll
+                for (int k = 0; k < V; ++k) o.v[k] += w.v[k] * old.v[k];
+                if (j > 0) stv<V>(st + (size_t)(j - 1) * H + i, old);       // the state moves on by one
+            }
+            const Vals<V> w = ldv<V>(cw + (size_t)back * H + i);
+#pragma unroll
+            for (int k = 0; k < V; ++k) o.v[k] += w.v[k] * cur.v[k];
+            if (back > 0) stv<V>(st + (size_t)(back - 1) * H + i, cur);
+        }
+        stv<V>(yr + i, o);
+    }
 }
 
 static int row_threads(int width, int n_rows) {
@@ -154,26 +225,45 @@ static int row_threads(int width, int n_rows) {
     return t;
 }
 
+template <typename TOut>
+static void postnorm_launch(int n_rows, int threads, size_t smem, cudaStream_t stream, float* h, const float* delta,
+                            int S, size_t dstride, const float* bias, const float* wu, float eps_u, const float* wn,
+                            float eps_n, TOut* y, const int* rows, int H, int write_h, const float* cw, int taps,
+                            float* state, size_t slot_stride, const int* seq_slot) {
+    if ((H & 3) == 0) {
+        auto k = postnorm_add_rmsnorm_kernel<TOut, 4>;
+        if (smem > 48 * 1024) cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        lumen_launch(k, dim3(n_rows), dim3(threads), smem, stream, h, delta, S, dstride, bias, wu, eps_u, wn, eps_n, y,
+                     rows, H, write_h, cw, taps, state, slot_stride, seq_slot);
+    } else {
+        auto k = postnorm_add_rmsnorm_kernel<TOut, 1>;
+        if (smem > 48 * 1024) cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        lumen_launch(k, dim3(n_rows), dim3(threads), smem, stream, h, delta, S, dstride, bias, wu, eps_u, wn, eps_n, y,
+                     rows, H, write_h, cw, taps, state, slot_stride, seq_slot);
+    }
+}
+
+// delta may be null (nothing pending: x = h). cw [taps][H] with its state folds the input
+// convolution of a step of single tokens in (row b = sequence b; not with `rows`).
 LUMEN_API int lumen_postnorm_add_rmsnorm(float* h, const float* delta, int n_delta, long long delta_stride,
                                          const float* bias, const float* wu, float eps_u, const float* wn,
                                          float eps_n, void* y, int y_is_bf16, const int* rows, int n_rows, int H,
-                                         int write_h, cudaStream_t stream) {
+                                         int write_h, const float* cw, int taps, float* state, long long slot_stride,
+                                         const int* seq_slot, cudaStream_t stream) {
     if (n_rows <= 0) return 0;
-    if (H <= 0 || n_delta < 1 || !delta || !wu || (wn && !y)) return LUMEN_ERR_BAD_ARGUMENT;
+    if (H <= 0 || (delta && (n_delta < 1 || !wu)) || (wn && !y)) return LUMEN_ERR_BAD_ARGUMENT;
+    if (cw && (rows || !wn || taps < 1 || taps > CANON_MAX_TAPS || (taps > 1 && (!state || !seq_slot))))
+        return LUMEN_ERR_BAD_ARGUMENT;
     const size_t smem = (size_t)H * sizeof(float);
     if (smem > 200 * 1024) return LUMEN_ERR_UNSUPPORTED;
-    const int threads = row_threads(H, n_rows);
-    if (y_is_bf16) {
-        auto k = postnorm_add_rmsnorm_kernel<__nv_bfloat16>;
-        if (smem > 48 * 1024) cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        lumen_launch(k, dim3(n_rows), dim3(threads), smem, stream, h, delta, n_delta, (size_t)delta_stride, bias, wu,
-                     eps_u, wn, eps_n, (__nv_bfloat16*)y, rows, H, write_h);
-    } else {
-        auto k = postnorm_add_rmsnorm_kernel<float>;
-        if (smem > 48 * 1024) cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        lumen_launch(k, dim3(n_rows), dim3(threads), smem, stream, h, delta, n_delta, (size_t)delta_stride, bias, wu,
-                     eps_u, wn, eps_n, (float*)y, rows, H, write_h);
-    }
+    const int threads = row_threads((H & 3) == 0 ? H / 4 : H, n_rows);
+    if (y_is_bf16)
+        postnorm_launch<__nv_bfloat16>(n_rows, threads, smem, stream, h, delta, n_delta, (size_t)delta_stride, bias, wu,
+                                       eps_u, wn, eps_n, (__nv_bfloat16*)y, rows, H, write_h, cw, taps, state,
+                                       (size_t)slot_stride, seq_slot);
+    else
+        postnorm_launch<float>(n_rows, threads, smem, stream, h, delta, n_delta, (size_t)delta_stride, bias, wu, eps_u,
+                               wn, eps_n, (float*)y, rows, H, write_h, cw, taps, state, (size_t)slot_stride, seq_slot);
     LUMEN_LAUNCH_CHECK();
     return 0;
 }
@@ -186,8 +276,7 @@ LUMEN_API int lumen_postnorm_add_rmsnorm(float* h, const float* delta, int n_del
 // among the first taps - 1 of its sequence in this step; blocks [N, N + B) take one sequence
 // each: its first tokens (which read the state) and the state's update, so that whatever
 // touches a sequence's state is read and then written by the same thread.
-#define CANON_MAX_TAPS 16
-template <typename TOut>
+template <typename TOut, int V>
 __global__ void canon_conv_kernel(const float* __restrict__ y, const float* __restrict__ w, int taps,
                                   float* __restrict__ state, size_t slot_stride, const int* __restrict__ tok_seq,
                                   const int* __restrict__ cu_q, const int* __restrict__ seq_slot, int N, int B,
@@ -200,10 +289,14 @@ __global__ void canon_conv_kernel(const float* __restrict__ y, const float* __re
         const int n = blk;
         const int i = n - cu_q[tok_seq[n]];
         if (i < back) return;
-        for (int c = threadIdx.x; c < H; c += blockDim.x) {
-            float acc = y[(size_t)n * H + c];
-            for (int j = 0; j < taps; ++j) acc += w[(size_t)j * H + c] * y[(size_t)(n - back + j) * H + c];
-            out[(size_t)n * H + c] = from_f32<TOut>(acc);
+        for (int c = threadIdx.x * V; c < H; c += blockDim.x * V) {
+            Vals<V> acc = ldv<V>(y + (size_t)n * H + c);
+            for (int j = 0; j < taps; ++j) {
+                const Vals<V> a = ldv<V>(w + (size_t)j * H + c), b = ldv<V>(y + (size_t)(n - back + j) * H + c);
+#pragma unroll
+                for (int k = 0; k < V; ++k) acc.v[k] += a.v[k] * b.v[k];
+            }
+            stv<V>(out + (size_t)n * H + c, acc);
         }
         return;
     }
@@ -245,12 +338,20 @@ LUMEN_API int lumen_canon_conv(const float* y, const float* w, int taps, float* 
                                int out_is_bf16, int H, cudaStream_t stream) {
     if (N <= 0) return 0;
     if (H <= 0 || B <= 0 || taps < 1 || taps > CANON_MAX_TAPS || (taps > 1 && !state)) return LUMEN_ERR_UNSUPPORTED;
-    const int threads = H >= 1024 ? 256 : 128;
-    if (out_is_bf16)
-        lumen_launch(canon_conv_kernel<__nv_bfloat16>, dim3(N + B), dim3(threads), 0, stream, y, w, taps, state,
+    const bool v4 = (H & 3) == 0;
+    int threads = ((v4 ? H / 4 : H) + 31) / 32 * 32;
+    threads = threads > 512 ? 512 : (threads < 64 ? 64 : threads);
+    if (out_is_bf16 && v4)
+        lumen_launch(canon_conv_kernel<__nv_bfloat16, 4>, dim3(N + B), dim3(threads), 0, stream, y, w, taps, state,
                      (size_t)slot_stride, tok_seq, cu_q, seq_slot, N, B, (__nv_bfloat16*)out, H);
+    else if (out_is_bf16)
+        lumen_launch(canon_conv_kernel<__nv_bfloat16, 1>, dim3(N + B), dim3(threads), 0, stream, y, w, taps, state,
+                     (size_t)slot_stride, tok_seq, cu_q, seq_slot, N, B, (__nv_bfloat16*)out, H);
+    else if (v4)
+        lumen_launch(canon_conv_kernel<float, 4>, dim3(N + B), dim3(threads), 0, stream, y, w, taps, state,
+                     (size_t)slot_stride, tok_seq, cu_q, seq_slot, N, B, (float*)out, H);
     else
-        lumen_launch(canon_conv_kernel<float>, dim3(N + B), dim3(threads), 0, stream, y, w, taps, state,
+        lumen_launch(canon_conv_kernel<float, 1>, dim3(N + B), dim3(threads), 0, stream, y, w, taps, state,
                      (size_t)slot_stride, tok_seq, cu_q, seq_slot, N, B, (float*)out, H);
     LUMEN_LAUNCH_CHECK();
     return 0;
@@ -259,7 +360,7 @@ LUMEN_API int lumen_canon_conv(const float* y, const float* w, int taps, float* 
 // ---------------------------------------------------------------- PolyNorm
 // out = a z / rms(z) + b z^2 / rms(z^2) + c z^3 / rms(z^3) + e, powers element by element,
 // rms(v) = sqrt(mean(v^2) + eps) over the row; act = (a, b, c, e) on the device.
-template <typename TOut>
+template <typename TOut, int V>
 __global__ void __launch_bounds__(1024)
 polynorm_kernel(const float* __restrict__ z, int S, size_t split_stride, const float* __restrict__ act, float eps,
                 TOut* __restrict__ out, int F) {
@@ -270,14 +371,21 @@ polynorm_kernel(const float* __restrict__ z, int S, size_t split_stride, const f
     const size_t row = blockIdx.x;
     const float* zr = z + row * F;
     float s2 = 0.0f, s4 = 0.0f, s6 = 0.0f;
-    for (int i = threadIdx.x; i < F; i += blockDim.x) {
-        float v = zr[i];
-        for (int s = 1; s < S; ++s) v += zr[(size_t)s * split_stride + i];
-        xs[i] = v;
-        const float v2 = v * v;
-        s2 += v2;
-        s4 += v2 * v2;
-        s6 += v2 * v2 * v2;
+    for (int i = threadIdx.x * V; i < F; i += blockDim.x * V) {
+        Vals<V> v = ldv<V>(zr + i);
+        for (int s = 1; s < S; ++s) {
+            const Vals<V> d = ldv<V>(zr + (size_t)s * split_stride + i);
+#pragma unroll
+            for (int k = 0; k < V; ++k) v.v[k] += d.v[k];
+        }
+        stv<V>(xs + i, v);
+#pragma unroll
+        for (int k = 0; k < V; ++k) {
+            const float v2 = v.v[k] * v.v[k];
+            s2 += v2;
+            s4 += v2 * v2;
+            s6 += v2 * v2 * v2;
+        }
     }
     s2 = block_sum(s2, red);
     s4 = block_sum(s4, red);
@@ -286,9 +394,29 @@ polynorm_kernel(const float* __restrict__ z, int S, size_t split_stride, const f
                 r3 = 1.0f / sqrtf(s6 / (float)F + eps);
     const float a = act[0], b = act[1], c = act[2], e = act[3];
     TOut* orow = out + row * F;
-    for (int i = threadIdx.x; i < F; i += blockDim.x) {
-        const float v = xs[i], v2 = v * v;
-        orow[i] = from_f32<TOut>(a * (v * r1) + b * (v2 * r2) + c * (v2 * v * r3) + e);
+    for (int i = threadIdx.x * V; i < F; i += blockDim.x * V) {
+        const Vals<V> x = ldv<V>(xs + i);
+        Vals<V> o;
+#pragma unroll
+        for (int k = 0; k < V; ++k) {
+            const float v = x.v[k], v2 = v * v;
+            o.v[k] = a * (v * r1) + b * (v2 * r2) + c * (v2 * v * r3) + e;
+        }
+        stv<V>(orow + i, o);
+    }
+}
+
+template <typename TOut>
+static void polynorm_launch(int N, int threads, size_t smem, cudaStream_t stream, const float* z, int S, size_t stride,
+                            const float* act, float eps, TOut* out, int F) {
+    if ((F & 3) == 0) {
+        auto k = polynorm_kernel<TOut, 4>;
+        if (smem > 48 * 1024) cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        lumen_launch(k, dim3(N), dim3(threads), smem, stream, z, S, stride, act, eps, out, F);
+    } else {
+        auto k = polynorm_kernel<TOut, 1>;
+        if (smem > 48 * 1024) cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        lumen_launch(k, dim3(N), dim3(threads), smem, stream, z, S, stride, act, eps, out, F);
     }
 }
 
@@ -298,17 +426,13 @@ LUMEN_API int lumen_polynorm(const float* z, int n_split, long long split_stride
     if (F <= 0 || n_split < 1 || !act) return LUMEN_ERR_BAD_ARGUMENT;
     const size_t smem = (size_t)F * sizeof(float);
     if (smem > 200 * 1024) return LUMEN_ERR_UNSUPPORTED;
-    const int threads = row_threads(F, N);
-    if (out_is_bf16) {
-        auto k = polynorm_kernel<__nv_bfloat16>;
-        if (smem > 48 * 1024) cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        lumen_launch(k, dim3(N), dim3(threads), smem, stream, z, n_split, (size_t)split_stride, act, eps,
-                     (__nv_bfloat16*)out, F);
-    } else {
-        auto k = polynorm_kernel<float>;
-        if (smem > 48 * 1024) cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        lumen_launch(k, dim3(N), dim3(threads), smem, stream, z, n_split, (size_t)split_stride, act, eps, (float*)out, F);
-    }
+    int threads = row_threads((F & 3) == 0 ? F / 4 : F, N);
+    if (N >= 2 * 148 && F >= 4096) threads = 512;
+    if (out_is_bf16)
+        polynorm_launch<__nv_bfloat16>(N, threads, smem, stream, z, n_split, (size_t)split_stride, act, eps,
+                                       (__nv_bfloat16*)out, F);
+    else
+        polynorm_launch<float>(N, threads, smem, stream, z, n_split, (size_t)split_stride, act, eps, (float*)out, F);
     LUMEN_LAUNCH_CHECK();
     return 0;
 }
@@ -320,7 +444,7 @@ LUMEN_API int lumen_polynorm(const float* z, int n_split, long long split_stride
 // (a null weight leaves the part as it is); q goes out as [N, Wq], the key and the value of
 // the token to its place in the paged cache: key tiles [page][kv head][PAGE][d], value tiles
 // [page][kv head][PAGE][dv].
-template <typename T>
+template <typename T, int V>
 __global__ void __launch_bounds__(1024)
 qkv_bias_norm_store_kernel(const float* __restrict__ qkv, int S, size_t split_stride, const float* __restrict__ bias,
                            const float* __restrict__ qw, const float* __restrict__ kw, float eps,
@@ -336,13 +460,24 @@ qkv_bias_norm_store_kernel(const float* __restrict__ qkv, int S, size_t split_st
     const int W = Wq + Wk + Wv;
     const float* row = qkv + (size_t)n * W;
     float sq = 0.0f, sk = 0.0f;
-    for (int i = threadIdx.x; i < W; i += blockDim.x) {
-        float x = row[i];
-        for (int s = 1; s < S; ++s) x += row[(size_t)s * split_stride + i];
-        if (bias) x += bias[i];
-        xs[i] = x;
-        if (i < Wq) sq += x * x;
-        else if (i < Wq + Wk) sk += x * x;
+    for (int i = threadIdx.x * V; i < W; i += blockDim.x * V) {
+        Vals<V> x = ldv<V>(row + i);
+        for (int s = 1; s < S; ++s) {
+            const Vals<V> p = ldv<V>(row + (size_t)s * split_stride + i);
+#pragma unroll
+            for (int k = 0; k < V; ++k) x.v[k] += p.v[k];
+        }
+        if (bias) {
+            const Vals<V> p = ldv<V>(bias + i);
+#pragma unroll
+            for (int k = 0; k < V; ++k) x.v[k] += p.v[k];
+        }
+        stv<V>(xs + i, x);
+        float ss = 0.0f;
+#pragma unroll
+        for (int k = 0; k < V; ++k) ss += x.v[k] * x.v[k];
+        if (i < Wq) sq += ss;                    // a group of V never straddles two parts
+        else if (i < Wq + Wk) sk += ss;
     }
     sq = block_sum(sq, red);
     sk = block_sum(sk, red);
@@ -351,18 +486,49 @@ qkv_bias_norm_store_kernel(const float* __restrict__ qkv, int S, size_t split_st
     const int pos = cache_pos[n];
     const int page = table[(size_t)tok_seq[n] * table_stride + pos / LUMEN_PAGE];
     const int r = pos % LUMEN_PAGE;
-    for (int i = threadIdx.x; i < W; i += blockDim.x) {
-        const float x = xs[i];
+    for (int i = threadIdx.x * V; i < W; i += blockDim.x * V) {
+        Vals<V> x = ldv<V>(xs + i);
         if (i < Wq) {
-            q_out[(size_t)n * Wq + i] = from_f32<T>(qw ? x * rq * qw[i] : x);
+            if (qw) {
+                const Vals<V> g = ldv<V>(qw + i);
+#pragma unroll
+                for (int k = 0; k < V; ++k) x.v[k] = x.v[k] * rq * g.v[k];
+            }
+            stv<V>(q_out + (size_t)n * Wq + i, x);
         } else if (i < Wq + Wk) {
             const int e = i - Wq, g = e / d, ee = e - g * d;
-            kc[((size_t)page * G + g) * LUMEN_PAGE * d + tile_offset(k_layout, r, ee, d)] =
-                from_f32<T>(kw ? x * rk * kw[e] : x);
+            if (kw) {
+                const Vals<V> gw = ldv<V>(kw + e);
+#pragma unroll
+                for (int k = 0; k < V; ++k) x.v[k] = x.v[k] * rk * gw.v[k];
+            }
+            T* tile = kc + ((size_t)page * G + g) * LUMEN_PAGE * d;
+            if (V == 1) tile[tile_offset(k_layout, r, ee, d)] = from_f32<T>(x.v[0]);
+            else stv<V>(tile + (size_t)r * d + ee, x);           // plain tiles only (the host sees to it)
         } else {
             const int e = i - Wq - Wk, g = e / dv, ee = e - g * dv;
-            vc[((size_t)page * G + g) * LUMEN_PAGE * dv + tile_offset(v_layout, r, ee, dv)] = from_f32<T>(x);
+            T* tile = vc + ((size_t)page * G + g) * LUMEN_PAGE * dv;
+            if (V == 1) tile[tile_offset(v_layout, r, ee, dv)] = from_f32<T>(x.v[0]);
+            else stv<V>(tile + (size_t)r * dv + ee, x);
         }
+    }
+}
+
+template <typename T>
+static void qkv_store_launch(bool v4, int N, int threads, size_t smem, cudaStream_t stream, const float* qkv, int S,
+                             size_t stride, const float* bias, const float* qw, const float* kw, float eps,
+                             const int* cache_pos, const int* tok_seq, const int* table, int table_stride, T* q_out,
+                             T* kc, T* vc, int Wq, int Wk, int Wv, int G, int d, int dv, int k_layout, int v_layout) {
+    if (v4) {
+        auto k = qkv_bias_norm_store_kernel<T, 4>;
+        if (smem > 48 * 1024) cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        lumen_launch(k, dim3(N), dim3(threads), smem, stream, qkv, S, stride, bias, qw, kw, eps, cache_pos, tok_seq, table,
+                     table_stride, q_out, kc, vc, Wq, Wk, Wv, G, d, dv, k_layout, v_layout);
+    } else {
+        auto k = qkv_bias_norm_store_kernel<T, 1>;
+        if (smem > 48 * 1024) cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        lumen_launch(k, dim3(N), dim3(threads), smem, stream, qkv, S, stride, bias, qw, kw, eps, cache_pos, tok_seq, table,
+                     table_stride, q_out, kc, vc, Wq, Wk, Wv, G, d, dv, k_layout, v_layout);
     }
 }
 
@@ -378,20 +544,17 @@ LUMEN_API int lumen_qkv_bias_norm_store(const float* qkv, int n_split, long long
     const int Wk = G * d, Wv = G * dv, W = Wq + Wk + Wv;
     const size_t smem = (size_t)W * sizeof(float);
     if (smem > 200 * 1024) return LUMEN_ERR_UNSUPPORTED;
-    const int threads = row_threads(W, N);
-    if (is_bf16) {
-        auto k = qkv_bias_norm_store_kernel<__nv_bfloat16>;
-        if (smem > 48 * 1024) cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        lumen_launch(k, dim3(N), dim3(threads), smem, stream, qkv, n_split, (size_t)split_stride, bias, qw, kw, eps,
-                     cache_pos, tok_seq, table, table_stride, (__nv_bfloat16*)q_out, (__nv_bfloat16*)kc,
-                     (__nv_bfloat16*)vc, Wq, Wk, Wv, G, d, dv, k_layout, v_layout);
-    } else {
-        auto k = qkv_bias_norm_store_kernel<float>;
-        if (smem > 48 * 1024) cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        lumen_launch(k, dim3(N), dim3(threads), smem, stream, qkv, n_split, (size_t)split_stride, bias, qw, kw, eps,
-                     cache_pos, tok_seq, table, table_stride, (float*)q_out, (float*)kc, (float*)vc, Wq, Wk, Wv, G, d,
-                     dv, k_layout, v_layout);
-    }
+    const bool v4 = (Wq & 3) == 0 && (d & 3) == 0 && (dv & 3) == 0 && k_layout == LUMEN_LAYOUT_LINEAR &&
+                    v_layout == LUMEN_LAYOUT_LINEAR;
+    const int threads = row_threads(v4 ? W / 4 : W, N);
+    if (is_bf16)
+        qkv_store_launch<__nv_bfloat16>(v4, N, threads, smem, stream, qkv, n_split, (size_t)split_stride, bias, qw, kw,
+                                        eps, cache_pos, tok_seq, table, table_stride, (__nv_bfloat16*)q_out,
+                                        (__nv_bfloat16*)kc, (__nv_bfloat16*)vc, Wq, Wk, Wv, G, d, dv, k_layout, v_layout);
+    else
+        qkv_store_launch<float>(v4, N, threads, smem, stream, qkv, n_split, (size_t)split_stride, bias, qw, kw, eps,
+                                cache_pos, tok_seq, table, table_stride, (float*)q_out, (float*)kc, (float*)vc, Wq, Wk,
+                                Wv, G, d, dv, k_layout, v_layout);
     LUMEN_LAUNCH_CHECK();
     return 0;
 }

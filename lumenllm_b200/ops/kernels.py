@@ -89,16 +89,21 @@ def embed_pos(tokens, table, scale, positions, pos_table, out=None):
 
 
 def postnorm_add_rmsnorm(h, delta, bias, w_update, eps_update, w_next, eps_next, out_dtype, rows=None,
-                         write_h=True):
+                         write_h=True, conv=None):
     """u = sum(delta[s]) (+ bias); x = h + rmsnorm(u) * w_update (stored back to h when write_h);
     y = rmsnorm(x) * w_next in out_dtype (None with w_next None). h float32 [N, H]; delta float32
-    [N, H] or [S, N, H]; rows int32 [W] gathers the rows to work on."""
+    [N, H] or [S, N, H], or None (nothing to add: x = h); rows int32 [W] gathers the rows to
+    work on. With conv = (weight float32 [taps, H], state float32 [slots, taps - 1, H] or None,
+    seq_slot int32 [N]) row b is the one new token of sequence b, and what goes out is the
+    convolution of canon_conv applied to y, the state moved on by one."""
     require(h, F32, "postnorm_add_rmsnorm.h")
-    require(w_update, F32, "postnorm_add_rmsnorm.w_update")
     N, H = h.shape
-    delta, S = _partials(delta, "postnorm_add_rmsnorm.delta")
-    if tuple(delta.shape[1:]) != (N, H) or w_update.numel() != H:
-        raise KernelError(f"postnorm_add_rmsnorm: delta {tuple(delta.shape)} / weight do not match h {(N, H)}")
+    S = 0
+    if delta is not None:
+        require(w_update, F32, "postnorm_add_rmsnorm.w_update")
+        delta, S = _partials(delta, "postnorm_add_rmsnorm.delta")
+        if tuple(delta.shape[1:]) != (N, H) or w_update.numel() != H:
+            raise KernelError(f"postnorm_add_rmsnorm: delta {tuple(delta.shape)} / weight do not match h {(N, H)}")
     for t, nm in ((bias, "bias"), (w_next, "w_next")):
         if t is not None:
             require(t, F32, f"postnorm_add_rmsnorm.{nm}")
@@ -108,12 +113,27 @@ def postnorm_add_rmsnorm(h, delta, bias, w_update, eps_update, w_next, eps_next,
     if rows is not None:
         require(rows, I32, "postnorm_add_rmsnorm.rows")
         n_rows = rows.numel()
+    cw = state = slots = None
+    taps, stride = 0, 0
+    if conv is not None:
+        cw, state, slots = conv
+        require(cw, F32, "postnorm_add_rmsnorm.conv weight")
+        require(slots, I32, "postnorm_add_rmsnorm.seq_slot")
+        taps = cw.shape[0]
+        if rows is not None or w_next is None or cw.shape[1] != H or not 1 <= taps <= CANON_MAX_TAPS or slots.numel() < N:
+            raise KernelError("postnorm_add_rmsnorm: the convolution takes whole steps of one token a sequence")
+        if taps > 1:
+            if state is None or state.dtype != F32 or tuple(state.shape[1:]) != (taps - 1, H) \
+                    or state.stride(2) != 1 or state.stride(1) != H:
+                raise KernelError(f"postnorm_add_rmsnorm: state must be float32 [slots, {taps - 1}, {H}] with dense rows")
+            stride = state.stride(0)
     y = torch.empty((n_rows, H), dtype=out_dtype, device=h.device) if w_next is not None else None
     f = fn("layer_ops", "lumen_postnorm_add_rmsnorm",
-           [P, P, c_int, c_longlong, P, P, c_float, P, c_float, P, c_int, P, c_int, c_int, c_int, P])
+           [P, P, c_int, c_longlong, P, P, c_float, P, c_float, P, c_int, P, c_int, c_int, c_int, P, c_int, P,
+            c_longlong, P, P])
     check(f(ptr(h), ptr(delta), S, N * H, ptr(bias), ptr(w_update), float(eps_update), ptr(w_next), float(eps_next),
-            ptr(y), _is_bf16(y) if y is not None else 0, ptr(rows), n_rows, H, 1 if write_h else 0, stream_ptr()),
-          "postnorm_add_rmsnorm")
+            ptr(y), _is_bf16(y) if y is not None else 0, ptr(rows), n_rows, H, 1 if write_h else 0, ptr(cw), taps,
+            ptr(state) if taps > 1 else 0, stride, ptr(slots), stream_ptr()), "postnorm_add_rmsnorm")
     return y
 
 

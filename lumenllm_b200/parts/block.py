@@ -95,15 +95,15 @@ class SandwichConvBlock:
     def forward(self, h, pending, ctx, entry):
         state = entry.state("block")
         r1 = self.conv_mixer.state_rows()
-        y = self.norm_mixer.forward(h, pending, torch.float32)
-        x = self.conv_mixer.forward(y, None if state is None or not r1 else state[:, :r1], ctx, self.runtime.dtype)
+        x = self.norm_mixer.forward_conv(h, pending, self.conv_mixer, None if state is None or not r1 else state[:, :r1],
+                                         ctx, self.runtime.dtype)
         a = self.mixer.forward(x, ctx, entry, bias_downstream=True)
         update = NormedUpdate(a, self.norm_mixer_out.weight, self.norm_mixer_out.eps,
                               getattr(self.mixer, "update_bias", None))
         if self.ffn is None:
             return h, update
-        y = self.norm_ffn.forward(h, update, torch.float32)
-        x = self.conv_ffn.forward(y, None if state is None or not self.conv_ffn.state_rows() else state[:, r1:],
-                                  ctx, self.runtime.dtype)
+        x = self.norm_ffn.forward_conv(h, update, self.conv_ffn,
+                                       None if state is None or not self.conv_ffn.state_rows() else state[:, r1:],
+                                       ctx, self.runtime.dtype)
         m = self.ffn.forward(x, ctx)
         return h, NormedUpdate(m, self.norm_ffn_out.weight, self.norm_ffn_out.eps)

@@ -44,3 +44,15 @@ class RMSNorm:
             return K.postnorm_add_rmsnorm(h, delta.delta, delta.bias, delta.weight, delta.eps, self.weight,
                                           self.eps, out_dtype, rows=rows, write_h=write_h)
         return K.add_rmsnorm(h, delta, self.weight, self.eps, out_dtype, rows=rows, write_h=write_h)
+
+    def forward_conv(self, h, delta, conv, state, ctx, out_dtype):
+        """The norm and, behind it, an input convolution (parts/conv.py) of the normed rows. A
+        step of one token a sequence whose pending update is a NormedUpdate (or nothing) is one
+        kernel; everything else is the norm, in float32, and then the convolution."""
+        if ctx.is_decode and (delta is None or isinstance(delta, NormedUpdate)):
+            d = delta
+            return K.postnorm_add_rmsnorm(h, None if d is None else d.delta, None if d is None else d.bias,
+                                          None if d is None else d.weight, 0.0 if d is None else d.eps,
+                                          self.weight, self.eps, out_dtype,
+                                          conv=(conv.weight, state, ctx.seq_slot))
+        return conv.forward(self.forward(h, delta, torch.float32), state, ctx, out_dtype)
