@@ -61,17 +61,19 @@ template <typename T>
 __global__ void __launch_bounds__(TS_THREADS)
 talk_scores_kernel(const T* __restrict__ q, const T* __restrict__ kcache, const int* __restrict__ table,
                    int table_stride, const int* __restrict__ tok_seq, const int* __restrict__ tok_pos,
-                   float* __restrict__ W, int row_stride, int n0, int H, int G, int d, int size, int keep,
-                   float scale, int layout) {
-    extern __shared__ __align__(16) float qs[];   // per * d floats
+                   float* __restrict__ W, float* __restrict__ stats, int row_stride, int n0, int H, int G, int d,
+                   int size, int keep, float scale, int layout) {
+    extern __shared__ __align__(16) float qs[];   // per * d floats, then per * TS_COLS scores
     pdl_wait();
     pdl_trigger();
     const int n = n0 + blockIdx.x, g = blockIdx.y, c0 = blockIdx.z * TS_COLS;
     const Sight s = sight_of(tok_pos[n], size, keep);
     if (c0 >= s.n) return;
     const int per = H / G;
+    float* sc = qs + per * d;
     const T* qrow = q + ((size_t)n * H + (size_t)g * per) * d;
     for (int e = threadIdx.x; e < per * d; e += TS_THREADS) qs[e] = to_f32(qrow[e]);
+    for (int e = threadIdx.x; e < per * TS_COLS; e += TS_THREADS) sc[e] = -INFINITY;
     __syncthreads();
     const int* bt = table + (size_t)tok_seq[n] * table_stride;
     const int sub = threadIdx.x & 3;
@@ -93,10 +95,11 @@ talk_scores_kernel(const T* __restrict__ q, const T* __restrict__ kcache, const 
 #pragma unroll
                 for (int hh = 0; hh < TS_MAX_PER; ++hh)
                     if (hh < per) {
-                        const float* qh = qs + hh * d + e;
+                        const float4 q0 = *reinterpret_cast<const float4*>(qs + hh * d + e);
+                        const float4 q1 = *reinterpret_cast<const float4*>(qs + hh * d + e + 4);
                         float a = acc[hh];
-#pragma unroll
-                        for (int k = 0; k < 8; ++k) a = fmaf(qh[k], kv[k], a);
+                        a = fmaf(q0.x, kv[0], a); a = fmaf(q0.y, kv[1], a); a = fmaf(q0.z, kv[2], a); a = fmaf(q0.w, kv[3], a);
+                        a = fmaf(q1.x, kv[4], a); a = fmaf(q1.y, kv[5], a); a = fmaf(q1.z, kv[6], a); a = fmaf(q1.w, kv[7], a);
                         acc[hh] = a;
                     }
             }
@@ -114,8 +117,24 @@ talk_scores_kernel(const T* __restrict__ q, const T* __restrict__ kcache, const 
                 float a = acc[hh];
                 a += __shfl_xor_sync(0xffffffffu, a, 1);
                 a += __shfl_xor_sync(0xffffffffu, a, 2);
-                if (sub == 0 && live) W[((size_t)(n - n0) * H + (size_t)g * per + hh) * row_stride + c] = a * scale;
+                if (sub == 0 && live) {
+                    W[((size_t)(n - n0) * H + (size_t)g * per + hh) * row_stride + c] = a * scale;
+                    sc[hh * TS_COLS + cc] = a * scale;
+                }
             }
+    }
+    // the chunk's maximum and sum of exponentials per head, for the mix kernel to put together
+    __syncthreads();
+    const int lane = threadIdx.x & 31, chunks = gridDim.z;
+    for (int hh = threadIdx.x >> 5; hh < per; hh += TS_THREADS / 32) {
+        const float a = sc[hh * TS_COLS + lane], b = sc[hh * TS_COLS + 32 + lane];
+        const float m = warp_max(fmaxf(a, b));
+        const float l = warp_sum(expf(a - m) + expf(b - m));      // columns beyond the token's give exp(-inf) = 0
+        if (lane == 0) {
+            float* st = stats + (((size_t)(n - n0) * H + (size_t)g * per + hh) * chunks + blockIdx.z) * 2;
+            st[0] = m;
+            st[1] = l;
+        }
     }
 }
 
@@ -125,8 +144,9 @@ talk_scores_kernel(const T* __restrict__ q, const T* __restrict__ kcache, const 
 // there each output head's mix, written over the scores.
 #define TM_THREADS 256
 #define TM_MAX_H 128
-// With HALF the mixed weights are written as bfloat16 over the front half of each row (the
-// tensor-core values kernel reads them so): column c then lands on the bytes of the float32
+// With HALF (prompt steps of the bfloat16 path) exponentials are the fast form, as in the
+// library's other serving attention kernels, and the mixed weights are written as bfloat16
+// over the front half of each row (the tensor-core values kernel reads them so): column c then lands on the bytes of the float32
 // columns c / 2, which belong to this or an earlier group of 256 columns, all read before the
 // barrier.
 // Without HALF the mix goes to a matrix of its own (Wout), and the blocks (token, group of 256
@@ -134,9 +154,9 @@ talk_scores_kernel(const T* __restrict__ q, const T* __restrict__ kcache, const 
 // tokens has too few tokens to fill the device with a block a token.
 template <bool HALF>
 __global__ void __launch_bounds__(TM_THREADS)
-talk_softmax_mix_kernel(float* __restrict__ W, float* __restrict__ Wout, int row_stride,
-                        const int* __restrict__ tok_pos, int n0, const float* __restrict__ talk, int H, int size,
-                        int keep) {
+talk_softmax_mix_kernel(float* __restrict__ W, float* __restrict__ Wout, const float* __restrict__ stats, int chunks,
+                        int row_stride, const int* __restrict__ tok_pos, int n0, const float* __restrict__ talk, int H,
+                        int size, int keep) {
     extern __shared__ __align__(16) float sm[];   // H * H (talk) + H * TM_THREADS (weights)
     __shared__ float mx[TM_MAX_H], inv[TM_MAX_H];
     float* tk = sm;
@@ -152,12 +172,21 @@ talk_softmax_mix_kernel(float* __restrict__ W, float* __restrict__ Wout, int row
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     for (int g = warp; g < H; g += TM_THREADS / 32) {
         const float* row = rows + (size_t)g * row_stride;
-        float m = -INFINITY;
-        for (int c = lane; c < s.n; c += 32) m = fmaxf(m, row[c]);
-        m = warp_max(m);
-        float l = 0.0f;
-        for (int c = lane; c < s.n; c += 32) l += expf(row[c] - m);
-        l = warp_sum(l);
+        float m = -INFINITY, l = 0.0f;
+        if (!HALF && stats) {
+            // per chunk of 64 columns the scores kernel left (maximum, sum of exponentials)
+            const float* st = stats + ((size_t)n * H + g) * chunks * 2;
+            const int used = (s.n + TS_COLS - 1) / TS_COLS;
+            for (int c = lane; c < used; c += 32) m = fmaxf(m, st[2 * c]);
+            m = warp_max(m);
+            for (int c = lane; c < used; c += 32) l += st[2 * c + 1] * expf(st[2 * c] - m);
+            l = warp_sum(l);
+        } else {
+            for (int c = lane; c < s.n; c += 32) m = fmaxf(m, row[c]);
+            m = warp_max(m);
+            for (int c = lane; c < s.n; c += 32) l += HALF ? __expf(row[c] - m) : expf(row[c] - m);
+            l = warp_sum(l);
+        }
         if (lane == 0) {
             mx[g] = m;
             inv[g] = 1.0f / l;
@@ -169,7 +198,8 @@ talk_softmax_mix_kernel(float* __restrict__ W, float* __restrict__ Wout, int row
         const int c = c0 + threadIdx.x;
         if (c < s.n)
             for (int g = 0; g < H; ++g)
-                ws[g * TM_THREADS + threadIdx.x] = expf(rows[(size_t)g * row_stride + c] - mx[g]) * inv[g];
+                ws[g * TM_THREADS + threadIdx.x] =
+                    (HALF ? __expf(rows[(size_t)g * row_stride + c] - mx[g]) : expf(rows[(size_t)g * row_stride + c] - mx[g])) * inv[g];
         // a thread reads back only what it wrote itself; the barrier is for the narrow form,
         // whose stores land on other threads' scores
         if (HALF) __syncthreads();
@@ -192,48 +222,105 @@ talk_softmax_mix_kernel(float* __restrict__ W, float* __restrict__ Wout, int row
 // [part][token][head][dv] that talk_parts_kernel adds in rising order.
 #define TV_THREADS 256
 #define TV_PART 128
-template <typename T>
+#define TV_MAX_PER 16
+// A lane's share of a value row: E consecutive values (E = 4 for values of up to 128, else 8).
+template <typename T, int E>
+__device__ __forceinline__ void load_vals(const T* p, float* v) {
+#pragma unroll
+    for (int k = 0; k < E; ++k) v[k] = to_f32(p[k]);
+}
+template <>
+__device__ __forceinline__ void load_vals<__nv_bfloat16, 4>(const __nv_bfloat16* p, float* v) {
+    const uint2 raw = *reinterpret_cast<const uint2*>(p);
+    const float2 a = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&raw.x));
+    const float2 b = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&raw.y));
+    v[0] = a.x; v[1] = a.y; v[2] = b.x; v[3] = b.y;
+}
+template <>
+__device__ __forceinline__ void load_vals<float, 4>(const float* p, float* v) {
+    const float4 a = *reinterpret_cast<const float4*>(p);
+    v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w;
+}
+
+template <typename T, int E, int PER>
 __global__ void __launch_bounds__(TV_THREADS)
 talk_values_kernel(const float* __restrict__ W, int row_stride, const T* __restrict__ vcache,
                    const int* __restrict__ table, int table_stride, const int* __restrict__ tok_seq,
                    const int* __restrict__ tok_pos, T* __restrict__ out, float* __restrict__ parts, int n0, int n_rows,
                    int H, int G, int dv, int size, int keep, int layout) {
-    __shared__ float acc_s[TV_THREADS / 32][256];
+    extern __shared__ __align__(16) float acc_s[];      // [warps][per][32 * E]
     pdl_wait();
     pdl_trigger();
-    const int n = blockIdx.x, h = blockIdx.y, z = blockIdx.z;
-    const int g = h / (H / G);
+    const int n = blockIdx.x, g = blockIdx.y, z = blockIdx.z;
+    const int per = H / G;
     const Sight s = sight_of(tok_pos[n0 + n], size, keep);
     const int c_lo = z * TV_PART, c_hi = min(s.n, c_lo + TV_PART);
     if (c_lo >= s.n) return;             // talk_parts_kernel reads only the parts a token has
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int* bt = table + (size_t)tok_seq[n0 + n] * table_stride;
-    const float* row = W + ((size_t)n * H + h) * row_stride;
-    float acc[8];
+    const float* rows = W + ((size_t)n * H + (size_t)g * per) * row_stride;
+    const int e0 = lane * E;
+    const bool mine = e0 < dv;
+    const bool whole = layout == LUMEN_LAYOUT_LINEAR && dv % E == 0;      // a lane's values move as one piece
+    float acc[PER][E];
 #pragma unroll
-    for (int k = 0; k < 8; ++k) acc[k] = 0.0f;
-#pragma unroll 4
+    for (int hh = 0; hh < PER; ++hh)
+#pragma unroll
+        for (int k = 0; k < E; ++k) acc[hh][k] = 0.0f;
+#pragma unroll 2
     for (int c = c_lo + warp; c < c_hi; c += TV_THREADS / 32) {
         const int j = key_of(s, c);
         const T* tile = vcache + ((size_t)bt[j / LUMEN_PAGE] * G + g) * LUMEN_PAGE * dv;
         const int r = j % LUMEN_PAGE;
-        const float w = row[c];
+        float v[E];
+        if (!mine) {
 #pragma unroll
-        for (int k = 0; k < 8; ++k) {
-            const int e = lane + 32 * k;
-            if (e < dv) acc[k] = fmaf(w, to_f32(tile[tile_offset(layout, r, e, dv)]), acc[k]);
+            for (int k = 0; k < E; ++k) v[k] = 0.0f;
+        } else if (whole) {
+            load_vals<T, E>(tile + (size_t)r * dv + e0, v);
+        } else {
+#pragma unroll
+            for (int k = 0; k < E; ++k) v[k] = e0 + k < dv ? to_f32(tile[tile_offset(layout, r, e0 + k, dv)]) : 0.0f;
         }
-    }
 #pragma unroll
-    for (int k = 0; k < 8; ++k) acc_s[warp][lane + 32 * k] = acc[k];
+        for (int hh = 0; hh < PER; ++hh)
+            if (hh < per) {
+                const float w = rows[(size_t)hh * row_stride + c];
+#pragma unroll
+                for (int k = 0; k < E; ++k) acc[hh][k] = fmaf(w, v[k], acc[hh][k]);
+            }
+    }
+    const int width = 32 * E;
+#pragma unroll
+    for (int hh = 0; hh < PER; ++hh)
+        if (hh < per)
+#pragma unroll
+            for (int k = 0; k < E; ++k) acc_s[((size_t)warp * per + hh) * width + e0 + k] = acc[hh][k];
     __syncthreads();
-    for (int e = threadIdx.x; e < dv; e += TV_THREADS) {
+    for (int i = threadIdx.x; i < per * dv; i += TV_THREADS) {
+        const int hh = i / dv, e = i - hh * dv;
         float a = 0.0f;
 #pragma unroll
-        for (int w8 = 0; w8 < TV_THREADS / 32; ++w8) a += acc_s[w8][e];
+        for (int w8 = 0; w8 < TV_THREADS / 32; ++w8) a += acc_s[((size_t)w8 * per + hh) * width + e];
+        const int h = g * per + hh;
         if (parts) parts[(((size_t)z * n_rows + n) * H + h) * dv + e] = a;
         else out[((size_t)(n0 + n) * H + h) * dv + e] = from_f32<T>(a);
     }
+}
+
+template <typename T, int E>
+static void launch_values(int per, dim3 grid, size_t smem, cudaStream_t stream, const float* W, int row_stride,
+                          const T* vc, const int* table, int table_stride, const int* tok_seq, const int* tok_pos,
+                          T* out, float* parts, int n0, int rows, int H, int G, int dv, int size, int keep, int layout) {
+#define LUMEN_TV(PER_)                                                                                               \
+    lumen_launch(talk_values_kernel<T, E, PER_>, grid, dim3(TV_THREADS), smem, stream, W, row_stride, vc, table,     \
+                 table_stride, tok_seq, tok_pos, out, parts, n0, rows, H, G, dv, size, keep, layout)
+    if (per <= 1) LUMEN_TV(1);
+    else if (per <= 2) LUMEN_TV(2);
+    else if (per <= 4) LUMEN_TV(4);
+    else if (per <= 8) LUMEN_TV(8);
+    else LUMEN_TV(16);
+#undef LUMEN_TV
 }
 
 template <typename T>
@@ -302,31 +389,55 @@ __device__ __forceinline__ void stage_rows(__nv_bfloat16* dst, int pitch, const 
     }
 }
 
+// The same for the 64 rows of a cache page, by asynchronous 16-byte copies (one group).
+__device__ __forceinline__ void stage_page_async(__nv_bfloat16* dst, int pitch, const __nv_bfloat16* src, int width) {
+    const int chunks = width / 8;
+    for (int i = threadIdx.x; i < LUMEN_PAGE * chunks; i += TP_THREADS) {
+        const int r = i / chunks, c = i - r * chunks;
+        asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(smem_u32(dst + (size_t)r * pitch + 8 * c)),
+                     "l"(src + (size_t)r * width + 8 * c)
+                     : "memory");
+    }
+    asm volatile("cp.async.commit_group;" ::: "memory");
+}
+__device__ __forceinline__ void async_wait_all() { asm volatile("cp.async.wait_group 0;" ::: "memory"); }
+
+// The pages a tile walks are dealt out over gridDim.z blocks (page k of the walk to block
+// k % gridDim.z): the scores of different pages do not meet. While a page is multiplied the
+// next one is on its way into the other half of the key buffer.
+#define TP_PAGES_A_BLOCK 4
 __global__ void __launch_bounds__(TP_THREADS)
 talk_scores_mma_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restrict__ kcache,
                        const int* __restrict__ table, int table_stride, const int* __restrict__ cu_q,
                        const int* __restrict__ seq_start, int B, float* __restrict__ W, int row_stride, int n0,
                        int n_rows, int H, int G, int d, int size, int keep, float scale) {
-    extern __shared__ __align__(16) __nv_bfloat16 sh[];     // queries [64][d + 8], keys [64][d + 8]
+    extern __shared__ __align__(16) __nv_bfloat16 sh[];     // queries [64][d + 8], keys 2 x [64][d + 8]
     pdl_wait();
     pdl_trigger();
     PromptTile t;
     if (!prompt_tile(blockIdx.x, cu_q, seq_start, B, size, keep, t)) return;
     if (t.tok0 + t.rows <= n0 || t.tok0 >= n0 + n_rows) return;
+    const int n_pages = t.kept_pages + t.hi_page - t.lo_page + 1;
+    if ((int)blockIdx.z >= n_pages) return;
     const int h = blockIdx.y, g = h / (H / G), pitch = d + 8;
     __nv_bfloat16* Qs = sh;
-    __nv_bfloat16* Ks = sh + TP_Q * pitch;
+    __nv_bfloat16* Kbuf = sh + TP_Q * pitch;
+    const int* bt = table + (size_t)t.b * table_stride;
+    auto page_of = [&](int pi) { return pi < t.kept_pages ? pi : t.lo_page + pi - t.kept_pages; };
+    stage_page_async(Kbuf, pitch, kcache + ((size_t)bt[page_of(blockIdx.z)] * G + g) * LUMEN_PAGE * d, d);
     stage_rows(Qs, pitch, q + ((size_t)t.tok0 * H + h) * d, (size_t)H * d, t.rows, d);
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-    const int* bt = table + (size_t)t.b * table_stride;
     const int a_row = warp * 16 + (lane & 7) + 8 * ((lane >> 3) & 1), a_col = 8 * (lane >> 4);
     const int b_row = (lane & 7) + 8 * (lane >> 4), b_col = 8 * ((lane >> 3) & 1);
-    const int n_pages = t.kept_pages + t.hi_page - t.lo_page + 1;
-    for (int pi = 0; pi < n_pages; ++pi) {
-        const int page_idx = pi < t.kept_pages ? pi : t.lo_page + pi - t.kept_pages;
-        __syncthreads();             // the tile before is read; the first time: nothing yet
-        stage_rows(Ks, pitch, kcache + ((size_t)bt[page_idx] * G + g) * LUMEN_PAGE * d, (size_t)d, LUMEN_PAGE, d);
-        __syncthreads();
+    int buf = 0;
+    for (int pi = blockIdx.z; pi < n_pages; pi += gridDim.z, buf ^= 1) {
+        const int page_idx = page_of(pi);
+        const __nv_bfloat16* Ks = Kbuf + (size_t)buf * LUMEN_PAGE * pitch;
+        async_wait_all();
+        __syncthreads();             // this page has arrived, and the other half has been read
+        if (pi + (int)gridDim.z < n_pages)
+            stage_page_async(Kbuf + (size_t)(buf ^ 1) * LUMEN_PAGE * pitch, pitch,
+                             kcache + ((size_t)bt[page_of(pi + gridDim.z)] * G + g) * LUMEN_PAGE * d, d);
         float acc[8][4];
 #pragma unroll
         for (int nt = 0; nt < 8; ++nt)
@@ -370,7 +481,7 @@ talk_values_mma_kernel(const float* __restrict__ W, int row_stride, const __nv_b
                        int H, int G, int size, int keep) {
     constexpr int dv = NT * 8, vpitch = dv + 8, ppitch = LUMEN_PAGE + 8;
     __shared__ __align__(16) __nv_bfloat16 Ps[TP_Q * ppitch];
-    __shared__ __align__(16) __nv_bfloat16 Vs[LUMEN_PAGE * vpitch];
+    __shared__ __align__(16) __nv_bfloat16 Vbuf[2 * LUMEN_PAGE * vpitch];      // this page's values and the next one's
     pdl_wait();
     pdl_trigger();
     PromptTile t;
@@ -387,9 +498,15 @@ talk_values_mma_kernel(const float* __restrict__ W, int row_stride, const __nv_b
 #pragma unroll
         for (int k = 0; k < 4; ++k) acc[nt][k] = 0.0f;
     const int n_pages = t.kept_pages + t.hi_page - t.lo_page + 1;
+    auto page_of = [&](int pi) { return pi < t.kept_pages ? pi : t.lo_page + pi - t.kept_pages; };
+    stage_page_async(Vbuf, vpitch, vcache + ((size_t)bt[page_of(0)] * G + g) * LUMEN_PAGE * dv, dv);
     for (int pi = 0; pi < n_pages; ++pi) {
-        const int page_idx = pi < t.kept_pages ? pi : t.lo_page + pi - t.kept_pages;
-        __syncthreads();
+        const int page_idx = page_of(pi);
+        const __nv_bfloat16* Vs = Vbuf + (size_t)(pi & 1) * LUMEN_PAGE * vpitch;
+        __syncthreads();             // the page before has been multiplied
+        if (pi + 1 < n_pages)
+            stage_page_async(Vbuf + (size_t)((pi + 1) & 1) * LUMEN_PAGE * vpitch, vpitch,
+                             vcache + ((size_t)bt[page_of(pi + 1)] * G + g) * LUMEN_PAGE * dv, dv);
         // the page's weights for the tile's queries: a warp takes its 16 queries one after the
         // other, a lane two neighbouring keys, so a query's 64 weights are one 128-byte read
 #pragma unroll 4
@@ -408,7 +525,9 @@ talk_values_mma_kernel(const float* __restrict__ W, int row_stride, const __nv_b
             }
             *reinterpret_cast<uint32_t*>(Ps + (size_t)i * ppitch + 2 * lane) = pack_bf16(w2[0], w2[1]);
         }
-        stage_rows(Vs, vpitch, vcache + ((size_t)bt[page_idx] * G + g) * LUMEN_PAGE * dv, (size_t)dv, LUMEN_PAGE, dv);
+        // this page's values were asked for a page ago; only the copies just issued may stay in flight
+        if (pi + 1 < n_pages) asm volatile("cp.async.wait_group 1;" ::: "memory");
+        else async_wait_all();
         __syncthreads();
 #pragma unroll
         for (int ks = 0; ks < LUMEN_PAGE / 16; ++ks) {
@@ -459,9 +578,12 @@ LUMEN_API int lumen_attn_talk_prompt(const void* q, const void* kc, const void* 
     if (!lumen_attn_talk_prompt_ok(H, G, d, dv) || B <= 0 || n_tiles <= 0 || rows_per_pass <= 0 || row_stride <= 0 ||
         size < 0 || keep < 0 || H > 65535)
         return LUMEN_ERR_UNSUPPORTED;
-    const size_t smem1 = (size_t)2 * TP_Q * (d + 8) * sizeof(__nv_bfloat16);
+    const size_t smem1 = (size_t)3 * TP_Q * (d + 8) * sizeof(__nv_bfloat16);
     const size_t smem2 = ((size_t)H * H + (size_t)H * TM_THREADS) * sizeof(float);
     if (smem2 > 200 * 1024) return LUMEN_ERR_UNSUPPORTED;
+    // pages a tile can walk: its window's (the tile's 64 queries wide), and the kept first keys'
+    const int walk = min(row_stride + 2 * LUMEN_PAGE, table_stride * LUMEN_PAGE) / LUMEN_PAGE + 2;
+    const dim3 grid1(n_tiles, H, max(1, min(64, (walk + TP_PAGES_A_BLOCK - 1) / TP_PAGES_A_BLOCK)));
     if (smem1 > 48 * 1024)
         cudaFuncSetAttribute(talk_scores_mma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem1);
     if (smem2 > 48 * 1024)
@@ -469,11 +591,11 @@ LUMEN_API int lumen_attn_talk_prompt(const void* q, const void* kc, const void* 
     const dim3 grid(n_tiles, H);
     for (int n0 = 0; n0 < N; n0 += rows_per_pass) {
         const int rows = min(rows_per_pass, N - n0);
-        lumen_launch(talk_scores_mma_kernel, grid, dim3(TP_THREADS), smem1, stream, (const __nv_bfloat16*)q,
+        lumen_launch(talk_scores_mma_kernel, grid1, dim3(TP_THREADS), smem1, stream, (const __nv_bfloat16*)q,
                      (const __nv_bfloat16*)kc, table, table_stride, cu_q, seq_start, B, W, row_stride, n0, rows, H, G, d,
                      size, keep, scale);
-        lumen_launch(talk_softmax_mix_kernel<true>, dim3(rows), dim3(TM_THREADS), smem2, stream, W, W, row_stride,
-                     tok_pos, n0, talk, H, size, keep);
+        lumen_launch(talk_softmax_mix_kernel<true>, dim3(rows), dim3(TM_THREADS), smem2, stream, W, W, (const float*)nullptr, 0,
+                     row_stride, tok_pos, n0, talk, H, size, keep);
 #define LUMEN_TALK_VALUES(NT_)                                                                                        \
     case NT_:                                                                                                         \
         launch_values_mma<NT_>(grid, stream, (const float*)W, row_stride, (const __nv_bfloat16*)vc, table,            \
@@ -496,15 +618,18 @@ LUMEN_API int lumen_attn_talk_prompt(const void* q, const void* kc, const void* 
 // [rows, H, row_stride] with rows >= min(N, rows_per_pass); parts: float32 [Z, rows, H, dv] when row_stride > TV_PART (Z parts), else null.
 template <typename T>
 static int attn_talk_run(const T* q, const T* kc, const T* vc, const int* table, int table_stride, const int* tok_seq,
-                         const int* tok_pos, const float* talk, T* out, float* W, float* W2, float* parts, int N,
+                         const int* tok_pos, const float* talk, T* out, float* W, float* W2, float* stats,
+                         float* parts, int N,
                          int rows_per_pass, int row_stride, int H, int G, int d, int dv, int size, int keep,
                          float scale, int k_layout, int v_layout, cudaStream_t stream) {
     const int per = H / G;
     const int chunks = (row_stride + TS_COLS - 1) / TS_COLS;
     const int Z = (row_stride + TV_PART - 1) / TV_PART;
-    const size_t smem1 = (size_t)per * d * sizeof(float);
+    const size_t smem1 = (size_t)per * (d + TS_COLS) * sizeof(float);
     const size_t smem2 = ((size_t)H * H + (size_t)H * TM_THREADS) * sizeof(float);
-    if (smem1 > 160 * 1024 || smem2 > 200 * 1024) return LUMEN_ERR_UNSUPPORTED;
+    const int E = (dv <= 128 && dv % 4 == 0) ? 4 : 8;
+    const size_t smem3 = (size_t)(TV_THREADS / 32) * per * 32 * E * sizeof(float);
+    if (smem1 > 160 * 1024 || smem2 > 200 * 1024 || smem3 > 48 * 1024) return LUMEN_ERR_UNSUPPORTED;
     if (smem1 > 48 * 1024)
         cudaFuncSetAttribute(talk_scores_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem1);
     if (smem2 > 48 * 1024)
@@ -512,12 +637,18 @@ static int attn_talk_run(const T* q, const T* kc, const T* vc, const int* table,
     for (int n0 = 0; n0 < N; n0 += rows_per_pass) {
         const int rows = min(rows_per_pass, N - n0);
         lumen_launch(talk_scores_kernel<T>, dim3(rows, G, chunks), dim3(TS_THREADS), smem1, stream, q, kc, table,
-                     table_stride, tok_seq, tok_pos, W, row_stride, n0, H, G, d, size, keep, scale, k_layout);
+                     table_stride, tok_seq, tok_pos, W, stats, row_stride, n0, H, G, d, size, keep, scale, k_layout);
         lumen_launch(talk_softmax_mix_kernel<false>, dim3(rows, (row_stride + TM_THREADS - 1) / TM_THREADS),
-                     dim3(TM_THREADS), smem2, stream, W, W2, row_stride, tok_pos, n0, talk, H, size, keep);
-        lumen_launch(talk_values_kernel<T>, dim3(rows, H, Z), dim3(TV_THREADS), 0, stream, (const float*)W2, row_stride,
-                     vc, table, table_stride, tok_seq, tok_pos, out, Z > 1 ? parts : (float*)nullptr, n0, rows, H, G, dv,
-                     size, keep, v_layout);
+                     dim3(TM_THREADS), smem2, stream, W, W2, (const float*)stats, chunks, row_stride, tok_pos, n0, talk, H,
+                     size, keep);
+        if (E == 4)
+            launch_values<T, 4>(per, dim3(rows, G, Z), smem3, stream, (const float*)W2, row_stride, vc, table,
+                                table_stride, tok_seq, tok_pos, out, Z > 1 ? parts : (float*)nullptr, n0, rows, H, G, dv,
+                                size, keep, v_layout);
+        else
+            launch_values<T, 8>(per, dim3(rows, G, Z), smem3, stream, (const float*)W2, row_stride, vc, table,
+                                table_stride, tok_seq, tok_pos, out, Z > 1 ? parts : (float*)nullptr, n0, rows, H, G, dv,
+                                size, keep, v_layout);
         if (Z > 1) {
             const size_t total = (size_t)rows * H * dv;
             lumen_launch(talk_parts_kernel<T>, dim3((unsigned)((total + 255) / 256)), dim3(256), 0, stream,
@@ -531,7 +662,7 @@ static int attn_talk_run(const T* q, const T* kc, const T* vc, const int* table,
 
 LUMEN_API int lumen_attn_talk(const void* q, const void* kc, const void* vc, const int* table, int table_stride,
                               const int* tok_seq, const int* tok_pos, const float* talk, void* out, float* W,
-                              float* W2, float* parts, int is_bf16, int N, int rows_per_pass, int row_stride, int H, int G, int d,
+                              float* W2, float* stats, float* parts, int is_bf16, int N, int rows_per_pass, int row_stride, int H, int G, int d,
                               int dv, int size, int keep, float scale, int k_layout, int v_layout,
                               cudaStream_t stream) {
     if (N <= 0) return 0;
@@ -541,13 +672,13 @@ LUMEN_API int lumen_attn_talk(const void* q, const void* kc, const void* vc, con
     if ((row_stride + TS_COLS - 1) / TS_COLS > 65535) return LUMEN_ERR_UNSUPPORTED;
     if ((k_layout == LUMEN_LAYOUT_SW128 && (!is_bf16 || d % 64)) || (v_layout == LUMEN_LAYOUT_SW128 && (!is_bf16 || dv % 64)))
         return LUMEN_ERR_UNSUPPORTED;
-    if ((row_stride > TV_PART && !parts) || !W || !W2 || W == W2) return LUMEN_ERR_BAD_ARGUMENT;
+    if ((row_stride > TV_PART && !parts) || !W || !W2 || W == W2 || !stats) return LUMEN_ERR_BAD_ARGUMENT;
     if (is_bf16)
         return attn_talk_run<__nv_bfloat16>((const __nv_bfloat16*)q, (const __nv_bfloat16*)kc, (const __nv_bfloat16*)vc,
-                                            table, table_stride, tok_seq, tok_pos, talk, (__nv_bfloat16*)out, W, W2, parts, N,
+                                            table, table_stride, tok_seq, tok_pos, talk, (__nv_bfloat16*)out, W, W2, stats, parts, N,
                                             rows_per_pass, row_stride, H, G, d, dv, size, keep, scale, k_layout,
                                             v_layout, stream);
     return attn_talk_run<float>((const float*)q, (const float*)kc, (const float*)vc, table, table_stride, tok_seq,
-                                tok_pos, talk, (float*)out, W, W2, parts, N, rows_per_pass, row_stride, H, G, d, dv, size,
+                                tok_pos, talk, (float*)out, W, W2, stats, parts, N, rows_per_pass, row_stride, H, G, d, dv, size,
                                 keep, scale, k_layout, v_layout, stream);
 }

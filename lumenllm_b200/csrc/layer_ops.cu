@@ -152,6 +152,18 @@ postnorm_add_rmsnorm_kernel(float* __restrict__ h, const float* __restrict__ del
     const int b = blockIdx.x;
     const int r = rows ? rows[b] : b;
     float* hr = h + (size_t)r * H;
+    // Few rows (wide blocks, one group of V values a thread): the stream's values and the norms'
+    // weights are asked for at once with the update's, not one round trip after the other.
+    const bool one = (int)blockDim.x * V >= H;
+    const int i1 = threadIdx.x * V;
+    Vals<V> h1, gu1, gn1;
+#pragma unroll
+    for (int k = 0; k < V; ++k) h1.v[k] = gu1.v[k] = gn1.v[k] = 0.0f;
+    if (one && i1 < H) {
+        h1 = ldv<V>(hr + i1);
+        if (delta) gu1 = ldv<V>(wu + i1);
+        if (wn) gn1 = ldv<V>(wn + i1);
+    }
     float ss = 0.0f;
     if (delta) {
         const float* dr = delta + (size_t)r * H;
@@ -176,9 +188,9 @@ postnorm_add_rmsnorm_kernel(float* __restrict__ h, const float* __restrict__ del
     const float su = 1.0f / sqrtf(ss / (float)H + eps_u);
     float ss2 = 0.0f;
     for (int i = threadIdx.x * V; i < H; i += blockDim.x * V) {
-        Vals<V> x = ldv<V>(hr + i);
+        Vals<V> x = one ? h1 : ldv<V>(hr + i);
         if (delta) {
-            const Vals<V> u = ldv<V>(xs + i), g = ldv<V>(wu + i);
+            const Vals<V> u = ldv<V>(xs + i), g = one ? gu1 : ldv<V>(wu + i);
 #pragma unroll
             for (int k = 0; k < V; ++k) x.v[k] += u.v[k] * su * g.v[k];
             if (write_h) stv<V>(hr + i, x);
@@ -194,7 +206,7 @@ postnorm_add_rmsnorm_kernel(float* __restrict__ h, const float* __restrict__ del
     float* st = cw && taps > 1 ? state + (size_t)seq_slot[b] * slot_stride : nullptr;
     const int back = taps - 1;
     for (int i = threadIdx.x * V; i < H; i += blockDim.x * V) {
-        const Vals<V> x = ldv<V>(xs + i), g = ldv<V>(wn + i);
+        const Vals<V> x = ldv<V>(xs + i), g = one ? gn1 : ldv<V>(wn + i);
         Vals<V> o;
 #pragma unroll
         for (int k = 0; k < V; ++k) o.v[k] = x.v[k] * sn * g.v[k];

@@ -220,6 +220,10 @@ ATTN_TALK_SCRATCH_BYTES = 256 << 20     # weights matrix of one pass over a step
 ATTN_TALK_PART = 128                    # columns a block of the values kernel walks (TV_PART)
 
 
+# Scratch of a prompt step's weights matrix; a step that needs more is worked on in passes over its
+# rows. (Passes small enough for the matrix to stay in the L2 between the three kernels were measured
+# and lost: 9.3 against 5.9 ms for eight layers at 2,048 tokens, since a pass then has fewer blocks
+# than the device holds and each block's walk over its pages takes as long as before.)
 ATTN_TALK_PROMPT_SCRATCH_BYTES = 1 << 30
 
 
@@ -259,7 +263,7 @@ def attn_talk(q, kcache, vcache, block_table, tok_seq, tok_pos, talk, window, ke
         if cu_q.numel() < n_seqs + 1 or seq_start.numel() < n_seqs:
             raise KernelError("attn_talk: metadata shorter than the batch")
         row_stride = (row_stride + 3) // 4 * 4
-        rows_per_pass = max(1, min(N, ATTN_TALK_PROMPT_SCRATCH_BYTES // (nq * row_stride * 4)))
+        rows_per_pass = min(N, max(64, ATTN_TALK_PROMPT_SCRATCH_BYTES // (nq * row_stride * 4) // 64 * 64))
         W = torch.empty((rows_per_pass, nq, row_stride), dtype=F32, device=q.device)
         f = fn("attn_talk", "lumen_attn_talk_prompt",
                [P, P, P, P, c_int, P, P, c_int, c_int, P, P, P, P, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
@@ -271,13 +275,15 @@ def attn_talk(q, kcache, vcache, block_table, tok_seq, tok_pos, talk, window, ke
         return out
     rows_per_pass = max(1, min(N, ATTN_TALK_SCRATCH_BYTES // (2 * nq * row_stride * 4)))
     W = torch.empty((2, rows_per_pass, nq, row_stride), dtype=F32, device=q.device)   # scores, mixed weights
+    chunks = -(-row_stride // 64)             # per 64 columns the scores kernel leaves (maximum, sum)
+    stats = torch.empty((rows_per_pass, nq, chunks, 2), dtype=F32, device=q.device)
     Z = -(-row_stride // ATTN_TALK_PART)
     parts = torch.empty((Z, rows_per_pass, nq, dv), dtype=F32, device=q.device) if Z > 1 else None
     f = fn("attn_talk", "lumen_attn_talk",
-           [P, P, P, P, c_int, P, P, P, P, P, P, P, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
-            c_float, c_int, c_int, P])
+           [P, P, P, P, c_int, P, P, P, P, P, P, P, P, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
+            c_int, c_float, c_int, c_int, P])
     check(f(ptr(q), ptr(kcache), ptr(vcache), ptr(block_table), block_table.stride(0), ptr(tok_seq), ptr(tok_pos),
-            ptr(talk), ptr(out), ptr(W[0]), ptr(W[1]), ptr(parts), _is_bf16(q), N, rows_per_pass, row_stride, nq, nkv, d, dv,
+            ptr(talk), ptr(out), ptr(W[0]), ptr(W[1]), ptr(stats), ptr(parts), _is_bf16(q), N, rows_per_pass, row_stride, nq, nkv, d, dv,
             int(window), int(keep_first), float(scale), int(k_layout), int(v_layout), stream_ptr()), "attn_talk")
     return out
 
