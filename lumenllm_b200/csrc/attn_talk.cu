@@ -78,6 +78,7 @@ talk_scores_kernel(const T* __restrict__ q, const T* __restrict__ kcache, const 
     const int* bt = table + (size_t)tok_seq[n] * table_stride;
     const int sub = threadIdx.x & 3;
     const bool vec = (d & 7) == 0 && layout == LUMEN_LAYOUT_LINEAR;
+#pragma unroll
     for (int cc = threadIdx.x >> 2; cc < TS_COLS; cc += TS_THREADS / 4) {
         const int c = c0 + cc;
         const bool live = c < s.n;       // every lane stays for the exchanges below
@@ -152,7 +153,10 @@ talk_scores_kernel(const T* __restrict__ q, const T* __restrict__ kcache, const 
 // Without HALF the mix goes to a matrix of its own (Wout), and the blocks (token, group of 256
 // columns) of a token each find the heads' maxima and sums for themselves: a step of single
 // tokens has too few tokens to fill the device with a block a token.
-template <bool HALF>
+// HR > 0 (at least the number of heads, a multiple of 4): a thread keeps its column's weights of
+// all heads in registers and reads the talk matrix four values at a time; HR = 0: any number of
+// heads, the weights go through shared memory.
+template <bool HALF, int HR>
 __global__ void __launch_bounds__(TM_THREADS)
 talk_softmax_mix_kernel(float* __restrict__ W, float* __restrict__ Wout, const float* __restrict__ stats, int chunks,
                         int row_stride, const int* __restrict__ tok_pos, int n0, const float* __restrict__ talk, int H,
@@ -160,8 +164,12 @@ talk_softmax_mix_kernel(float* __restrict__ W, float* __restrict__ Wout, const f
     extern __shared__ __align__(16) float sm[];   // H * H (talk) + H * TM_THREADS (weights)
     __shared__ float mx[TM_MAX_H], inv[TM_MAX_H];
     float* tk = sm;
-    float* ws = sm + H * H;
-    for (int i = threadIdx.x; i < H * H; i += TM_THREADS) tk[i] = talk[i];    // never changes
+    float* ws = sm + H * H;                   // used with HR = 0 only
+    const int tw = HR > 0 ? HR : H;           // width of a row of the talk matrix in shared memory
+    for (int i = threadIdx.x; i < H * tw; i += TM_THREADS) {
+        const int hh = i / tw, g = i - hh * tw;
+        tk[i] = g < H ? talk[hh * H + g] : 0.0f;                              // never changes
+    }
     pdl_wait();
     pdl_trigger();
     const int n = blockIdx.x;
@@ -196,10 +204,21 @@ talk_softmax_mix_kernel(float* __restrict__ W, float* __restrict__ Wout, const f
     const int c_begin = HALF ? 0 : (int)blockIdx.y * TM_THREADS, c_end = HALF ? s.n : min(s.n, c_begin + TM_THREADS);
     for (int c0 = c_begin; c0 < c_end; c0 += TM_THREADS) {
         const int c = c0 + threadIdx.x;
-        if (c < s.n)
-            for (int g = 0; g < H; ++g)
-                ws[g * TM_THREADS + threadIdx.x] =
-                    (HALF ? __expf(rows[(size_t)g * row_stride + c] - mx[g]) : expf(rows[(size_t)g * row_stride + c] - mx[g])) * inv[g];
+        float p[HR > 0 ? HR : 1];
+        if (c < s.n) {
+            if (HR > 0) {
+#pragma unroll
+                for (int g = 0; g < HR; ++g) {
+                    const float x = g < H ? rows[(size_t)g * row_stride + c] - mx[g] : 0.0f;
+                    p[g] = g < H ? (HALF ? __expf(x) : expf(x)) * inv[g] : 0.0f;
+                }
+            } else {
+                for (int g = 0; g < H; ++g) {
+                    const float x = rows[(size_t)g * row_stride + c] - mx[g];
+                    ws[g * TM_THREADS + threadIdx.x] = (HALF ? __expf(x) : expf(x)) * inv[g];
+                }
+            }
+        }
         // a thread reads back only what it wrote itself; the barrier is for the narrow form,
         // whose stores land on other threads' scores
         if (HALF) __syncthreads();
@@ -207,12 +226,43 @@ talk_softmax_mix_kernel(float* __restrict__ W, float* __restrict__ Wout, const f
             for (int h = 0; h < H; ++h) {
                 const float* t = tk + h * H;
                 float a = 0.0f;
-                for (int g = 0; g < H; ++g) a = fmaf(t[g], ws[g * TM_THREADS + threadIdx.x], a);
+                if (HR > 0) {
+                    // the talk matrix lies in rows of HR values (zeros behind the heads)
+                    const float4* t4 = reinterpret_cast<const float4*>(tk + h * HR);
+#pragma unroll
+                    for (int g4 = 0; g4 < HR / 4; ++g4) {
+                        const float4 w = t4[g4];
+                        a = fmaf(w.x, p[4 * g4], a);
+                        a = fmaf(w.y, p[4 * g4 + 1], a);
+                        a = fmaf(w.z, p[4 * g4 + 2], a);
+                        a = fmaf(w.w, p[4 * g4 + 3], a);
+                    }
+                } else {
+                    for (int g = 0; g < H; ++g) a = fmaf(t[g], ws[g * TM_THREADS + threadIdx.x], a);
+                }
                 if (HALF) reinterpret_cast<__nv_bfloat16*>(rows + (size_t)h * row_stride)[c] = __float2bfloat16_rn(a);
                 else rows_out[(size_t)h * row_stride + c] = a;
             }
         if (HALF) __syncthreads();
     }
+}
+
+template <bool HALF>
+static void launch_mix(dim3 grid, cudaStream_t stream, float* W, float* Wout, const float* stats, int chunks,
+                       int row_stride, const int* tok_pos, int n0, const float* talk, int H, int size, int keep) {
+#define LUMEN_MIX(HR_, SMEM_)                                                                                          \
+    do {                                                                                                               \
+        auto k = talk_softmax_mix_kernel<HALF, HR_>;                                                                   \
+        const size_t smem = (SMEM_);                                                                                   \
+        if (smem > 48 * 1024) cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);         \
+        lumen_launch(k, grid, dim3(TM_THREADS), smem, stream, W, Wout, stats, chunks, row_stride, tok_pos, n0, talk, H, \
+                     size, keep);                                                                                      \
+    } while (0)
+    if (H <= 8) LUMEN_MIX(8, (size_t)H * 8 * sizeof(float));
+    else if (H <= 16) LUMEN_MIX(16, (size_t)H * 16 * sizeof(float));
+    else if (H <= 32) LUMEN_MIX(32, (size_t)H * 32 * sizeof(float));
+    else LUMEN_MIX(0, ((size_t)H * H + (size_t)H * TM_THREADS) * sizeof(float));
+#undef LUMEN_MIX
 }
 
 // ---------------------------------------------------------------- 3. values
@@ -267,28 +317,47 @@ talk_values_kernel(const float* __restrict__ W, int row_stride, const T* __restr
     for (int hh = 0; hh < PER; ++hh)
 #pragma unroll
         for (int k = 0; k < E; ++k) acc[hh][k] = 0.0f;
-#pragma unroll 2
-    for (int c = c_lo + warp; c < c_hi; c += TV_THREADS / 32) {
-        const int j = key_of(s, c);
-        const T* tile = vcache + ((size_t)bt[j / LUMEN_PAGE] * G + g) * LUMEN_PAGE * dv;
-        const int r = j % LUMEN_PAGE;
+    // Lane l fetches, for the warp's l-th column, the page and row of its key and the heads'
+    // weights; the walk below takes them from there, so that no load in it waits for another.
+    constexpr int COLS = TV_PART / (TV_THREADS / 32);
+    int my_page = 0, my_r = 0;
+    float my_w[PER];
+#pragma unroll
+    for (int hh = 0; hh < PER; ++hh) my_w[hh] = 0.0f;
+    {
+        const int c = c_lo + warp + (TV_THREADS / 32) * lane;
+        if (lane < COLS && c < c_hi) {
+            const int j = key_of(s, c);
+            my_page = bt[j / LUMEN_PAGE];
+            my_r = j % LUMEN_PAGE;
+#pragma unroll
+            for (int hh = 0; hh < PER; ++hh)
+                if (hh < per) my_w[hh] = rows[(size_t)hh * row_stride + c];
+        }
+    }
+#pragma unroll 4
+    for (int k = 0; k < COLS; ++k) {
+        if (c_lo + warp + (TV_THREADS / 32) * k >= c_hi) break;          // the same for the whole warp
+        const int page = __shfl_sync(0xffffffffu, my_page, k), r = __shfl_sync(0xffffffffu, my_r, k);
+        const T* tile = vcache + ((size_t)page * G + g) * LUMEN_PAGE * dv;
         float v[E];
         if (!mine) {
 #pragma unroll
-            for (int k = 0; k < E; ++k) v[k] = 0.0f;
+            for (int e = 0; e < E; ++e) v[e] = 0.0f;
         } else if (whole) {
             load_vals<T, E>(tile + (size_t)r * dv + e0, v);
         } else {
 #pragma unroll
-            for (int k = 0; k < E; ++k) v[k] = e0 + k < dv ? to_f32(tile[tile_offset(layout, r, e0 + k, dv)]) : 0.0f;
+            for (int e = 0; e < E; ++e) v[e] = e0 + e < dv ? to_f32(tile[tile_offset(layout, r, e0 + e, dv)]) : 0.0f;
         }
 #pragma unroll
-        for (int hh = 0; hh < PER; ++hh)
+        for (int hh = 0; hh < PER; ++hh) {
+            const float w = __shfl_sync(0xffffffffu, my_w[hh], k);
             if (hh < per) {
-                const float w = rows[(size_t)hh * row_stride + c];
 #pragma unroll
-                for (int k = 0; k < E; ++k) acc[hh][k] = fmaf(w, v[k], acc[hh][k]);
+                for (int e = 0; e < E; ++e) acc[hh][e] = fmaf(w, v[e], acc[hh][e]);
             }
+        }
     }
     const int width = 32 * E;
 #pragma unroll
@@ -500,6 +569,29 @@ talk_values_mma_kernel(const float* __restrict__ W, int row_stride, const __nv_b
     const int n_pages = t.kept_pages + t.hi_page - t.lo_page + 1;
     auto page_of = [&](int pi) { return pi < t.kept_pages ? pi : t.lo_page + pi - t.kept_pages; };
     stage_page_async(Vbuf, vpitch, vcache + ((size_t)bt[page_of(0)] * G + g) * LUMEN_PAGE * dv, dv);
+    // A page's weights for the tile's queries: a warp takes its 16 queries one after the other,
+    // a lane two neighbouring keys, so a query's 64 weights are one 128-byte read; zero where the
+    // key is out of the query's sight.
+    unsigned short pw[32];         // raw bfloat16 bits: nothing waits for the loads before the tile is written
+    auto fetch_weights = [&](int page_idx) {
+#pragma unroll
+        for (int rr = 0; rr < 16; ++rr) {
+            const int i = warp * 16 + rr, tok = t.tok0 + i;
+            const bool live = i < t.rows && tok >= n0 && tok < n0 + n_rows;
+            const Sight s = sight_of(t.p0 + (live ? i : 0), size, keep);
+            const __nv_bfloat16* row =
+                reinterpret_cast<const __nv_bfloat16*>(W + ((size_t)(live ? tok - n0 : 0) * H + h) * row_stride);
+#pragma unroll
+            for (int k = 0; k < 2; ++k) {
+                const int j = page_idx * LUMEN_PAGE + 2 * lane + k;
+                const bool seen = live && j <= t.p0 + i && (j >= s.lo || j < s.kept);
+                unsigned short bits = 0;
+                if (seen) bits = reinterpret_cast<const unsigned short*>(row)[j < s.kept ? j : s.kept + (j - s.lo)];
+                pw[2 * rr + k] = bits;
+            }
+        }
+    };
+    fetch_weights(page_of(0));
     for (int pi = 0; pi < n_pages; ++pi) {
         const int page_idx = page_of(pi);
         const __nv_bfloat16* Vs = Vbuf + (size_t)(pi & 1) * LUMEN_PAGE * vpitch;
@@ -507,28 +599,16 @@ talk_values_mma_kernel(const float* __restrict__ W, int row_stride, const __nv_b
         if (pi + 1 < n_pages)
             stage_page_async(Vbuf + (size_t)((pi + 1) & 1) * LUMEN_PAGE * vpitch, vpitch,
                              vcache + ((size_t)bt[page_of(pi + 1)] * G + g) * LUMEN_PAGE * dv, dv);
-        // the page's weights for the tile's queries: a warp takes its 16 queries one after the
-        // other, a lane two neighbouring keys, so a query's 64 weights are one 128-byte read
-#pragma unroll 4
-        for (int rr = 0; rr < 16; ++rr) {
-            const int i = warp * 16 + rr, tok = t.tok0 + i;
-            const bool live = i < t.rows && tok >= n0 && tok < n0 + n_rows;
-            const Sight s = sight_of(t.p0 + (live ? i : 0), size, keep);
-            const __nv_bfloat16* row =
-                reinterpret_cast<const __nv_bfloat16*>(W + ((size_t)(live ? tok - n0 : 0) * H + h) * row_stride);
-            float w2[2];
+        // the page's weights, fetched while the page before was multiplied (below), into their tile
 #pragma unroll
-            for (int k = 0; k < 2; ++k) {
-                const int j = page_idx * LUMEN_PAGE + 2 * lane + k;
-                const bool seen = live && j <= t.p0 + i && (j >= s.lo || j < s.kept);
-                w2[k] = seen ? __bfloat162float(row[j < s.kept ? j : s.kept + (j - s.lo)]) : 0.0f;
-            }
-            *reinterpret_cast<uint32_t*>(Ps + (size_t)i * ppitch + 2 * lane) = pack_bf16(w2[0], w2[1]);
-        }
+        for (int rr = 0; rr < 16; ++rr)
+            *reinterpret_cast<uint32_t*>(Ps + (size_t)(warp * 16 + rr) * ppitch + 2 * lane) =
+                (uint32_t)pw[2 * rr] | ((uint32_t)pw[2 * rr + 1] << 16);
         // this page's values were asked for a page ago; only the copies just issued may stay in flight
         if (pi + 1 < n_pages) asm volatile("cp.async.wait_group 1;" ::: "memory");
         else async_wait_all();
         __syncthreads();
+        if (pi + 1 < n_pages) fetch_weights(page_of(pi + 1));       // in flight while this page is multiplied
 #pragma unroll
         for (int ks = 0; ks < LUMEN_PAGE / 16; ++ks) {
             uint32_t a[4];
@@ -586,16 +666,13 @@ LUMEN_API int lumen_attn_talk_prompt(const void* q, const void* kc, const void* 
     const dim3 grid1(n_tiles, H, max(1, min(64, (walk + TP_PAGES_A_BLOCK - 1) / TP_PAGES_A_BLOCK)));
     if (smem1 > 48 * 1024)
         cudaFuncSetAttribute(talk_scores_mma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem1);
-    if (smem2 > 48 * 1024)
-        cudaFuncSetAttribute(talk_softmax_mix_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem2);
     const dim3 grid(n_tiles, H);
     for (int n0 = 0; n0 < N; n0 += rows_per_pass) {
         const int rows = min(rows_per_pass, N - n0);
         lumen_launch(talk_scores_mma_kernel, grid1, dim3(TP_THREADS), smem1, stream, (const __nv_bfloat16*)q,
                      (const __nv_bfloat16*)kc, table, table_stride, cu_q, seq_start, B, W, row_stride, n0, rows, H, G, d,
                      size, keep, scale);
-        lumen_launch(talk_softmax_mix_kernel<true>, dim3(rows), dim3(TM_THREADS), smem2, stream, W, W, (const float*)nullptr, 0,
-                     row_stride, tok_pos, n0, talk, H, size, keep);
+        launch_mix<true>(dim3(rows), stream, W, W, (const float*)nullptr, 0, row_stride, tok_pos, n0, talk, H, size, keep);
 #define LUMEN_TALK_VALUES(NT_)                                                                                        \
     case NT_:                                                                                                         \
         launch_values_mma<NT_>(grid, stream, (const float*)W, row_stride, (const __nv_bfloat16*)vc, table,            \
@@ -632,15 +709,12 @@ static int attn_talk_run(const T* q, const T* kc, const T* vc, const int* table,
     if (smem1 > 160 * 1024 || smem2 > 200 * 1024 || smem3 > 48 * 1024) return LUMEN_ERR_UNSUPPORTED;
     if (smem1 > 48 * 1024)
         cudaFuncSetAttribute(talk_scores_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem1);
-    if (smem2 > 48 * 1024)
-        cudaFuncSetAttribute(talk_softmax_mix_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem2);
     for (int n0 = 0; n0 < N; n0 += rows_per_pass) {
         const int rows = min(rows_per_pass, N - n0);
         lumen_launch(talk_scores_kernel<T>, dim3(rows, G, chunks), dim3(TS_THREADS), smem1, stream, q, kc, table,
                      table_stride, tok_seq, tok_pos, W, stats, row_stride, n0, H, G, d, size, keep, scale, k_layout);
-        lumen_launch(talk_softmax_mix_kernel<false>, dim3(rows, (row_stride + TM_THREADS - 1) / TM_THREADS),
-                     dim3(TM_THREADS), smem2, stream, W, W2, (const float*)stats, chunks, row_stride, tok_pos, n0, talk, H,
-                     size, keep);
+        launch_mix<false>(dim3(rows, (row_stride + TM_THREADS - 1) / TM_THREADS), stream, W, W2, (const float*)stats,
+                          chunks, row_stride, tok_pos, n0, talk, H, size, keep);
         if (E == 4)
             launch_values<T, 4>(per, dim3(rows, G, Z), smem3, stream, (const float*)W2, row_stride, vc, table,
                                 table_stride, tok_seq, tok_pos, out, Z > 1 ? parts : (float*)nullptr, n0, rows, H, G, dv,
