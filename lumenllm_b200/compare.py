@@ -85,6 +85,7 @@ def measure(config, batch, steps, warmup, seed=0):
     import torch
     from .engine import Engine, StepEntry
     from .sampling import SamplingConfig
+    t_begin = time.perf_counter()
     eng = Engine.from_random(config, seed=seed, std=0.02, dtype="bfloat16",
                              max_tokens=batch * CONTEXT, max_slots=max(batch, 8), context_size=CONTEXT)
     eng.graphs.min_width = CONTEXT // 64
@@ -118,13 +119,12 @@ def measure(config, batch, steps, warmup, seed=0):
         tok = eng.run_device(entries, cfgs, us, tokens_on_device=tok)
     torch.cuda.synchronize()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    t0 = time.perf_counter()
     e0.record()
     for _ in range(steps):
         tok = eng.run_device(entries, cfgs, us, tokens_on_device=tok)
     e1.record()
     torch.cuda.synchronize()
-    window = (t0, time.perf_counter())
+    window = (t_begin, time.perf_counter())       # the clocks' samples of the whole measurement
     eng.check_kernels()
     decode_ms = e0.elapsed_time(e1) / steps
     per_replay = getattr(getattr(eng.graphs, "last", None), "kernels_per_replay", 0)
@@ -159,3 +159,45 @@ def run(design, sizes, batch, steps, warmup):
             torch.cuda.empty_cache()
         out[name] = row
     return out
+
+
+def steps_main(argv=None) -> int:
+    """`python -m lumenllm_b200.compare --design dabevik|qwen3 --kind prompt|decode [--size 2k]
+    [--layers 2] [--batch 8]`: a few steps of one kind launched kernel by kernel, for a profiler's
+    launch list (nothing is timed here)."""
+    import argparse
+    import torch
+    from .engine import Engine, StepEntry
+    from .sampling import SamplingConfig
+    ap = argparse.ArgumentParser(prog="lumenllm_b200.compare")
+    ap.add_argument("--design", default="dabevik", choices=["dabevik", "qwen3"])
+    ap.add_argument("--kind", default="decode", choices=["prompt", "decode"])
+    ap.add_argument("--size", default="2k", choices=sorted(SIZES))
+    ap.add_argument("--layers", type=int, default=2)
+    ap.add_argument("--batch", type=int, default=8)
+    a = ap.parse_args(argv)
+    s = dict(SIZES[a.size], layers=a.layers)
+    cfg = dabevik_config(s) if a.design == "dabevik" else qwen3_config(s)
+    eng = Engine.from_random(cfg, seed=0, std=0.02, dtype="bfloat16", max_tokens=a.batch * CONTEXT,
+                             max_slots=max(a.batch, 8), context_size=CONTEXT, use_graphs=False)
+    g = torch.Generator().manual_seed(1)
+    rand = lambda n: torch.randint(0, eng.vocab_size, (n,), generator=g).tolist()
+    if a.kind == "prompt":
+        for _ in range(2):
+            slot = eng.alloc_slot()
+            eng.step([StepEntry(slot, rand(PROMPT_TOKENS), [PROMPT_TOKENS - 1])])
+            eng.free_slot(slot)
+    else:
+        slots = [eng.alloc_slot() for _ in range(a.batch)]
+        eng.step([StepEntry(sl, rand(1500), []) for sl in slots])
+        for _ in range(3):
+            eng.run_device([(sl, [1]) for sl in slots], [SamplingConfig()] * a.batch, [0.0] * a.batch)
+    torch.cuda.synchronize()
+    eng.check_kernels()
+    print("ok")
+    return 0
+
+
+if __name__ == "__main__":
+    import sys
+    sys.exit(steps_main())

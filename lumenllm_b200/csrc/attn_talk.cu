@@ -64,8 +64,8 @@ talk_scores_kernel(const T* __restrict__ q, const T* __restrict__ kcache, const 
                    float* __restrict__ W, float* __restrict__ stats, int row_stride, int n0, int H, int G, int d,
                    int size, int keep, float scale, int layout) {
     extern __shared__ __align__(16) float qs[];   // per * d floats, then per * TS_COLS scores
+    pdl_trigger();       // the kernel behind may come to rest and wait; it still waits for this one's end
     pdl_wait();
-    pdl_trigger();
     const int n = n0 + blockIdx.x, g = blockIdx.y, c0 = blockIdx.z * TS_COLS;
     const Sight s = sight_of(tok_pos[n], size, keep);
     if (c0 >= s.n) return;
@@ -170,8 +170,8 @@ talk_softmax_mix_kernel(float* __restrict__ W, float* __restrict__ Wout, const f
         const int hh = i / tw, g = i - hh * tw;
         tk[i] = g < H ? talk[hh * H + g] : 0.0f;                              // never changes
     }
+    pdl_trigger();       // the kernel behind may come to rest and wait; it still waits for this one's end
     pdl_wait();
-    pdl_trigger();
     const int n = blockIdx.x;
     const Sight s = sight_of(tok_pos[n0 + n], size, keep);
     if (!HALF && (int)blockIdx.y * TM_THREADS >= s.n) return;
@@ -254,7 +254,7 @@ static void launch_mix(dim3 grid, cudaStream_t stream, float* W, float* Wout, co
     do {                                                                                                               \
         auto k = talk_softmax_mix_kernel<HALF, HR_>;                                                                   \
         const size_t smem = (SMEM_);                                                                                   \
-        if (smem > 48 * 1024) cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);         \
+        if (smem > 40 * 1024) cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);         \
         lumen_launch(k, grid, dim3(TM_THREADS), smem, stream, W, Wout, stats, chunks, row_stride, tok_pos, n0, talk, H, \
                      size, keep);                                                                                      \
     } while (0)
@@ -299,8 +299,8 @@ talk_values_kernel(const float* __restrict__ W, int row_stride, const T* __restr
                    const int* __restrict__ tok_pos, T* __restrict__ out, float* __restrict__ parts, int n0, int n_rows,
                    int H, int G, int dv, int size, int keep, int layout) {
     extern __shared__ __align__(16) float acc_s[];      // [warps][per][32 * E]
+    pdl_trigger();       // the kernel behind may come to rest and wait; it still waits for this one's end
     pdl_wait();
-    pdl_trigger();
     const int n = blockIdx.x, g = blockIdx.y, z = blockIdx.z;
     const int per = H / G;
     const Sight s = sight_of(tok_pos[n0 + n], size, keep);
@@ -396,8 +396,8 @@ template <typename T>
 __global__ void talk_parts_kernel(const float* __restrict__ parts, int Z, size_t part_stride,
                                   const int* __restrict__ tok_pos, int n0, int row_width, int size, int keep,
                                   T* __restrict__ out, size_t total) {
+    pdl_trigger();       // the kernel behind may come to rest and wait; it still waits for this one's end
     pdl_wait();
-    pdl_trigger();
     const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
     if (i >= total) return;
     const int n = (int)(i / row_width);
@@ -481,8 +481,8 @@ talk_scores_mma_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16*
                        const int* __restrict__ seq_start, int B, float* __restrict__ W, int row_stride, int n0,
                        int n_rows, int H, int G, int d, int size, int keep, float scale) {
     extern __shared__ __align__(16) __nv_bfloat16 sh[];     // queries [64][d + 8], keys 2 x [64][d + 8]
+    pdl_trigger();       // the kernel behind may come to rest and wait; it still waits for this one's end
     pdl_wait();
-    pdl_trigger();
     PromptTile t;
     if (!prompt_tile(blockIdx.x, cu_q, seq_start, B, size, keep, t)) return;
     if (t.tok0 + t.rows <= n0 || t.tok0 >= n0 + n_rows) return;
@@ -551,8 +551,8 @@ talk_values_mma_kernel(const float* __restrict__ W, int row_stride, const __nv_b
     constexpr int dv = NT * 8, vpitch = dv + 8, ppitch = LUMEN_PAGE + 8;
     __shared__ __align__(16) __nv_bfloat16 Ps[TP_Q * ppitch];
     __shared__ __align__(16) __nv_bfloat16 Vbuf[2 * LUMEN_PAGE * vpitch];      // this page's values and the next one's
+    pdl_trigger();       // the kernel behind may come to rest and wait; it still waits for this one's end
     pdl_wait();
-    pdl_trigger();
     PromptTile t;
     if (!prompt_tile(blockIdx.x, cu_q, seq_start, B, size, keep, t)) return;
     if (t.tok0 + t.rows <= n0 || t.tok0 >= n0 + n_rows) return;
@@ -664,7 +664,7 @@ LUMEN_API int lumen_attn_talk_prompt(const void* q, const void* kc, const void* 
     // pages a tile can walk: its window's (the tile's 64 queries wide), and the kept first keys'
     const int walk = min(row_stride + 2 * LUMEN_PAGE, table_stride * LUMEN_PAGE) / LUMEN_PAGE + 2;
     const dim3 grid1(n_tiles, H, max(1, min(64, (walk + TP_PAGES_A_BLOCK - 1) / TP_PAGES_A_BLOCK)));
-    if (smem1 > 48 * 1024)
+    if (smem1 > 40 * 1024)
         cudaFuncSetAttribute(talk_scores_mma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem1);
     const dim3 grid(n_tiles, H);
     for (int n0 = 0; n0 < N; n0 += rows_per_pass) {
@@ -707,7 +707,7 @@ static int attn_talk_run(const T* q, const T* kc, const T* vc, const int* table,
     const int E = (dv <= 128 && dv % 4 == 0) ? 4 : 8;
     const size_t smem3 = (size_t)(TV_THREADS / 32) * per * 32 * E * sizeof(float);
     if (smem1 > 160 * 1024 || smem2 > 200 * 1024 || smem3 > 48 * 1024) return LUMEN_ERR_UNSUPPORTED;
-    if (smem1 > 48 * 1024)
+    if (smem1 > 40 * 1024)
         cudaFuncSetAttribute(talk_scores_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem1);
     for (int n0 = 0; n0 < N; n0 += rows_per_pass) {
         const int rows = min(rows_per_pass, N - n0);

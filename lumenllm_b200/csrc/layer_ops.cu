@@ -244,12 +244,12 @@ static void postnorm_launch(int n_rows, int threads, size_t smem, cudaStream_t s
                             float* state, size_t slot_stride, const int* seq_slot) {
     if ((H & 3) == 0) {
         auto k = postnorm_add_rmsnorm_kernel<TOut, 4>;
-        if (smem > 48 * 1024) cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (smem > 40 * 1024) cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         lumen_launch(k, dim3(n_rows), dim3(threads), smem, stream, h, delta, S, dstride, bias, wu, eps_u, wn, eps_n, y,
                      rows, H, write_h, cw, taps, state, slot_stride, seq_slot);
     } else {
         auto k = postnorm_add_rmsnorm_kernel<TOut, 1>;
-        if (smem > 48 * 1024) cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (smem > 40 * 1024) cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         lumen_launch(k, dim3(n_rows), dim3(threads), smem, stream, h, delta, S, dstride, bias, wu, eps_u, wn, eps_n, y,
                      rows, H, write_h, cw, taps, state, slot_stride, seq_slot);
     }
@@ -284,20 +284,77 @@ LUMEN_API int lumen_postnorm_add_rmsnorm(float* h, const float* delta, int n_del
 // out[t] = y[t] + sum_{j < taps} w[j] * y[t - taps + 1 + j] on every channel, over the tokens of
 // ONE sequence; what lies before the step's first token comes from the sequence's state (its
 // last taps - 1 inputs, zeros for a new sequence), and the state is moved on to the step's end.
-// w is stored [taps][H]. Blocks [0, N) take one token each and leave at once if the token is
-// among the first taps - 1 of its sequence in this step; blocks [N, N + B) take one sequence
-// each: its first tokens (which read the state) and the state's update, so that whatever
-// touches a sequence's state is read and then written by the same thread.
+// w is stored [taps][H]. The first blocks take one token each (eight in steps of many tokens) and
+// skip tokens among the first taps - 1 of their sequence in this step; the blocks behind them take
+// the sequences: a sequence's first tokens (which read the state) and the state's update, so that
+// whatever touches a channel of a sequence's state is read and then written by the same thread.
+#define CANON_FAST_TAPS 8        // up to this many taps the blocks of prompt steps take several tokens each
+#define CANON_GROUP 8
 template <typename TOut, int V>
 __global__ void canon_conv_kernel(const float* __restrict__ y, const float* __restrict__ w, int taps,
                                   float* __restrict__ state, size_t slot_stride, const int* __restrict__ tok_seq,
                                   const int* __restrict__ cu_q, const int* __restrict__ seq_slot, int N, int B,
-                                  TOut* __restrict__ out, int H) {
+                                  TOut* __restrict__ out, int H, int group, int token_blocks) {
     pdl_trigger();
     pdl_wait();
     const int blk = blockIdx.x;
     const int back = taps - 1;
-    if (blk < N) {
+    if (group > 1 && blk < token_blocks) {
+        // `group` consecutive tokens a block (the host launches N / group of these blocks and
+        // numbers the sequence blocks behind them): a thread walks down its channels with the last
+        // inputs in registers, so a row is read once and not once for every tap.
+        const int first = blk * CANON_GROUP;
+        if (first >= N) return;
+        unsigned takes = 0;               // which of the block's tokens are not among their sequence's first
+#pragma unroll
+        for (int t = 0; t < CANON_GROUP; ++t)
+            if (first + t < N && first + t - cu_q[tok_seq[first + t]] >= back) takes |= 1u << t;
+        for (int c = threadIdx.x * V; c < H; c += blockDim.x * V) {
+            Vals<V> win[CANON_FAST_TAPS - 1], wv[CANON_FAST_TAPS], cur[CANON_GROUP];
+            // every row the block needs is asked for before the first one is used
+#pragma unroll
+            for (int t = 0; t < CANON_GROUP; ++t)
+                if (first + t < N) cur[t] = ldv<V>(y + (size_t)(first + t) * H + c);
+#pragma unroll
+            for (int j = 0; j < CANON_FAST_TAPS - 1; ++j)
+                if (j < back) {
+                    if (first - back + j >= 0) win[j] = ldv<V>(y + (size_t)(first - back + j) * H + c);
+                    else
+#pragma unroll
+                        for (int k = 0; k < V; ++k) win[j].v[k] = 0.0f;    // before the step: only tokens that the sequence blocks take read it
+                }
+#pragma unroll
+            for (int j = 0; j < CANON_FAST_TAPS; ++j)
+                if (j < taps) wv[j] = ldv<V>(w + (size_t)j * H + c);
+#pragma unroll
+            for (int t = 0; t < CANON_GROUP; ++t) {
+                if (first + t >= N) break;
+                if (takes >> t & 1u) {
+                    Vals<V> acc = cur[t];
+#pragma unroll
+                    for (int j = 0; j < CANON_FAST_TAPS - 1; ++j)
+                        if (j < back) {
+#pragma unroll
+                            for (int k = 0; k < V; ++k) acc.v[k] += wv[j].v[k] * win[j].v[k];
+                        }
+#pragma unroll
+                    for (int j = 0; j < CANON_FAST_TAPS; ++j)
+                        if (j == back) {
+#pragma unroll
+                            for (int k = 0; k < V; ++k) acc.v[k] += wv[j].v[k] * cur[t].v[k];
+                        }
+                    stv<V>(out + (size_t)(first + t) * H + c, acc);
+                }
+#pragma unroll
+                for (int j = 0; j < CANON_FAST_TAPS - 2; ++j) win[j] = win[j + 1];
+#pragma unroll
+                for (int j = 0; j < CANON_FAST_TAPS - 1; ++j)
+                    if (j == back - 1) win[j] = cur[t];
+            }
+        }
+        return;
+    }
+    if (group <= 1 && blk < N) {
         const int n = blk;
         const int i = n - cu_q[tok_seq[n]];
         if (i < back) return;
@@ -312,12 +369,16 @@ __global__ void canon_conv_kernel(const float* __restrict__ y, const float* __re
         }
         return;
     }
-    const int b = blk - N;
+    // a sequence's channels are spread over as many blocks as give every thread one channel:
+    // a thread's walk is a chain of loads, and one block a sequence would be the step's last to end
+    const int cpb = (H + (int)blockDim.x - 1) / (int)blockDim.x;
+    const int hb = blk - (group > 1 ? token_blocks : N);
+    const int b = hb / cpb;
     const int n0 = cu_q[b], q = cu_q[b + 1] - n0;
     if (q <= 0 || back == 0) return;
     float* st = state + (size_t)seq_slot[b] * slot_stride;
     const int m = q < back ? q : back;
-    for (int c = threadIdx.x; c < H; c += blockDim.x) {
+    for (int c = (hb - b * cpb) * (int)blockDim.x + threadIdx.x; c < H; c += H) {
         float win[CANON_MAX_TAPS];
 #pragma unroll
         for (int k = 0; k < CANON_MAX_TAPS - 1; ++k) win[k] = k < back ? st[(size_t)k * H + c] : 0.0f;
@@ -353,18 +414,23 @@ LUMEN_API int lumen_canon_conv(const float* y, const float* w, int taps, float* 
     const bool v4 = (H & 3) == 0;
     int threads = ((v4 ? H / 4 : H) + 31) / 32 * 32;
     threads = threads > 512 ? 512 : (threads < 64 ? 64 : threads);
+    // many tokens and few taps: blocks of CANON_GROUP tokens; else a token a block
+    const int group = (N >= 4 * 148 && taps <= CANON_FAST_TAPS) ? CANON_GROUP : 1;
+    const int token_blocks = group > 1 ? (N + group - 1) / group : N;
+    if (group > 1 && threads > 256) threads = 256;
+    const dim3 grid(token_blocks + B * ((H + threads - 1) / threads));
     if (out_is_bf16 && v4)
-        lumen_launch(canon_conv_kernel<__nv_bfloat16, 4>, dim3(N + B), dim3(threads), 0, stream, y, w, taps, state,
-                     (size_t)slot_stride, tok_seq, cu_q, seq_slot, N, B, (__nv_bfloat16*)out, H);
+        lumen_launch(canon_conv_kernel<__nv_bfloat16, 4>, grid, dim3(threads), 0, stream, y, w, taps, state,
+                     (size_t)slot_stride, tok_seq, cu_q, seq_slot, N, B, (__nv_bfloat16*)out, H, group, token_blocks);
     else if (out_is_bf16)
-        lumen_launch(canon_conv_kernel<__nv_bfloat16, 1>, dim3(N + B), dim3(threads), 0, stream, y, w, taps, state,
-                     (size_t)slot_stride, tok_seq, cu_q, seq_slot, N, B, (__nv_bfloat16*)out, H);
+        lumen_launch(canon_conv_kernel<__nv_bfloat16, 1>, grid, dim3(threads), 0, stream, y, w, taps, state,
+                     (size_t)slot_stride, tok_seq, cu_q, seq_slot, N, B, (__nv_bfloat16*)out, H, group, token_blocks);
     else if (v4)
-        lumen_launch(canon_conv_kernel<float, 4>, dim3(N + B), dim3(threads), 0, stream, y, w, taps, state,
-                     (size_t)slot_stride, tok_seq, cu_q, seq_slot, N, B, (float*)out, H);
+        lumen_launch(canon_conv_kernel<float, 4>, grid, dim3(threads), 0, stream, y, w, taps, state,
+                     (size_t)slot_stride, tok_seq, cu_q, seq_slot, N, B, (float*)out, H, group, token_blocks);
     else
-        lumen_launch(canon_conv_kernel<float, 1>, dim3(N + B), dim3(threads), 0, stream, y, w, taps, state,
-                     (size_t)slot_stride, tok_seq, cu_q, seq_slot, N, B, (float*)out, H);
+        lumen_launch(canon_conv_kernel<float, 1>, grid, dim3(threads), 0, stream, y, w, taps, state,
+                     (size_t)slot_stride, tok_seq, cu_q, seq_slot, N, B, (float*)out, H, group, token_blocks);
     LUMEN_LAUNCH_CHECK();
     return 0;
 }
@@ -423,11 +489,11 @@ static void polynorm_launch(int N, int threads, size_t smem, cudaStream_t stream
                             const float* act, float eps, TOut* out, int F) {
     if ((F & 3) == 0) {
         auto k = polynorm_kernel<TOut, 4>;
-        if (smem > 48 * 1024) cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (smem > 40 * 1024) cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         lumen_launch(k, dim3(N), dim3(threads), smem, stream, z, S, stride, act, eps, out, F);
     } else {
         auto k = polynorm_kernel<TOut, 1>;
-        if (smem > 48 * 1024) cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (smem > 40 * 1024) cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         lumen_launch(k, dim3(N), dim3(threads), smem, stream, z, S, stride, act, eps, out, F);
     }
 }
@@ -533,12 +599,12 @@ static void qkv_store_launch(bool v4, int N, int threads, size_t smem, cudaStrea
                              T* kc, T* vc, int Wq, int Wk, int Wv, int G, int d, int dv, int k_layout, int v_layout) {
     if (v4) {
         auto k = qkv_bias_norm_store_kernel<T, 4>;
-        if (smem > 48 * 1024) cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (smem > 40 * 1024) cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         lumen_launch(k, dim3(N), dim3(threads), smem, stream, qkv, S, stride, bias, qw, kw, eps, cache_pos, tok_seq, table,
                      table_stride, q_out, kc, vc, Wq, Wk, Wv, G, d, dv, k_layout, v_layout);
     } else {
         auto k = qkv_bias_norm_store_kernel<T, 1>;
-        if (smem > 48 * 1024) cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (smem > 40 * 1024) cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         lumen_launch(k, dim3(N), dim3(threads), smem, stream, qkv, S, stride, bias, qw, kw, eps, cache_pos, tok_seq, table,
                      table_stride, q_out, kc, vc, Wq, Wk, Wv, G, d, dv, k_layout, v_layout);
     }

@@ -122,6 +122,37 @@ def test_input_convolution_in_any_portions(taps):
             cache.free_slot(s)
 
 
+@pytest.mark.parametrize("taps", [1, 3, 8, 11])
+def test_input_convolution_of_long_prompts(taps):
+    """Steps of many tokens (blocks then take several tokens each, up to eight taps): sequences
+    that start and continue inside the step, their borders anywhere among the blocks' tokens."""
+    from lumenllm_b200.cache import KVCache
+    from lumenllm_b200.config import PartSpec
+    from lumenllm_b200.engine.context import StepEntry, build_context
+    from lumenllm_b200.parts import build_part
+    rt = runtime(F32)
+    D = 72
+    g = torch.Generator().manual_seed(100 + taps)
+    w = {"c": torch.randn(D, taps, generator=g).to(BF16).cuda()}
+    part = build_part("input_conv", PartSpec("causal_depthwise", {"size": D, "taps": taps, "tensor": "c"}), w, rt)
+    shapes = {(0, "block"): ((taps - 1, D), F32)} if taps > 1 else {}
+    cache = KVCache({}, 8192, 4, 8192, dtype=F32, device=rt.device, state_shapes=shapes)
+    seqs = [torch.randn(n, D, generator=g) for n in (701, 5, 450)]
+    refs = [P.input_convolution(s, w["c"].float().cpu()) for s in seqs]
+    slots = [cache.alloc_slot() for _ in seqs]
+    at = [0, 0, 0]
+    for cuts in ([3, 2, 300], [398, 3, 150], [300, 0, 0]):
+        members = [b for b in range(3) if cuts[b]]
+        ctx, _ = build_context(cache, rt, [StepEntry(slots[b], [0] * cuts[b]) for b in members])
+        y = torch.cat([seqs[b][at[b]:at[b] + cuts[b]] for b in members]).cuda()
+        out = part.forward(y, cache.state.of(0, "block"), ctx, F32).cpu()
+        ref = torch.cat([refs[b][at[b]:at[b] + cuts[b]] for b in members])
+        assert float((out - ref).abs().max()) < 1e-5, (taps, cuts)
+        for b in members:
+            cache.commit(slots[b], cuts[b])
+            at[b] += cuts[b]
+
+
 @pytest.mark.parametrize("dtype", [F32, BF16])
 def test_update_normed_before_the_add_then_the_next_norm(dtype):
     from lumenllm_b200.ops import kernels as K
@@ -246,7 +277,7 @@ def test_one_loud_key_at_every_edge_of_sight(dtype, decode):
 def test_whole_prompts(name, dtype, models, plain):
     from lumenllm_b200.engine import StepEntry
     eng = engine_of(models, name, dtype)
-    for toks in tokens_of(SMALL[name], (1, 2, 37, 201), seed=1):
+    for toks in tokens_of(SMALL[name], (1, 2, 37, 201) + ((640,) if name == "Z" else ()), seed=1):
         slot = eng.alloc_slot()
         got = eng.step([StepEntry(slot, toks, list(range(len(toks))))])
         eng.free_slot(slot)
