@@ -62,16 +62,19 @@ __global__ void __launch_bounds__(TS_THREADS)
 talk_scores_kernel(const T* __restrict__ q, const T* __restrict__ kcache, const int* __restrict__ table,
                    int table_stride, const int* __restrict__ tok_seq, const int* __restrict__ tok_pos,
                    float* __restrict__ W, float* __restrict__ stats, int row_stride, int n0, int H, int G, int d,
-                   int size, int keep, float scale, int layout) {
+                   int size, int keep, float scale, int layout, int hsplit) {
     extern __shared__ __align__(16) float qs[];   // per * d floats, then per * TS_COLS scores
     pdl_trigger();       // the kernel behind may come to rest and wait; it still waits for this one's end
     pdl_wait();
-    const int n = n0 + blockIdx.x, g = blockIdx.y, c0 = blockIdx.z * TS_COLS;
+    // blockIdx.y counts (kv head, part of its heads): a kv head with more than TS_MAX_PER heads is
+    // taken by `hsplit` blocks, each with an equal share of the heads
+    const int n = n0 + blockIdx.x, g = blockIdx.y / hsplit, c0 = blockIdx.z * TS_COLS;
     const Sight s = sight_of(tok_pos[n], size, keep);
     if (c0 >= s.n) return;
-    const int per = H / G;
+    const int per = H / G / hsplit;
+    const int h0 = g * (H / G) + (blockIdx.y % hsplit) * per;       // the block's first head
     float* sc = qs + per * d;
-    const T* qrow = q + ((size_t)n * H + (size_t)g * per) * d;
+    const T* qrow = q + ((size_t)n * H + h0) * d;
     for (int e = threadIdx.x; e < per * d; e += TS_THREADS) qs[e] = to_f32(qrow[e]);
     for (int e = threadIdx.x; e < per * TS_COLS; e += TS_THREADS) sc[e] = -INFINITY;
     __syncthreads();
@@ -119,7 +122,7 @@ talk_scores_kernel(const T* __restrict__ q, const T* __restrict__ kcache, const 
                 a += __shfl_xor_sync(0xffffffffu, a, 1);
                 a += __shfl_xor_sync(0xffffffffu, a, 2);
                 if (sub == 0 && live) {
-                    W[((size_t)(n - n0) * H + (size_t)g * per + hh) * row_stride + c] = a * scale;
+                    W[((size_t)(n - n0) * H + h0 + hh) * row_stride + c] = a * scale;
                     sc[hh * TS_COLS + cc] = a * scale;
                 }
             }
@@ -132,7 +135,7 @@ talk_scores_kernel(const T* __restrict__ q, const T* __restrict__ kcache, const 
         const float m = warp_max(fmaxf(a, b));
         const float l = warp_sum(expf(a - m) + expf(b - m));      // columns beyond the token's give exp(-inf) = 0
         if (lane == 0) {
-            float* st = stats + (((size_t)(n - n0) * H + (size_t)g * per + hh) * chunks + blockIdx.z) * 2;
+            float* st = stats + (((size_t)(n - n0) * H + h0 + hh) * chunks + blockIdx.z) * 2;
             st[0] = m;
             st[1] = l;
         }
@@ -297,18 +300,19 @@ __global__ void __launch_bounds__(TV_THREADS)
 talk_values_kernel(const float* __restrict__ W, int row_stride, const T* __restrict__ vcache,
                    const int* __restrict__ table, int table_stride, const int* __restrict__ tok_seq,
                    const int* __restrict__ tok_pos, T* __restrict__ out, float* __restrict__ parts, int n0, int n_rows,
-                   int H, int G, int dv, int size, int keep, int layout) {
+                   int H, int G, int dv, int size, int keep, int layout, int hsplit) {
     extern __shared__ __align__(16) float acc_s[];      // [warps][per][32 * E]
     pdl_trigger();       // the kernel behind may come to rest and wait; it still waits for this one's end
     pdl_wait();
-    const int n = blockIdx.x, g = blockIdx.y, z = blockIdx.z;
-    const int per = H / G;
+    const int n = blockIdx.x, g = blockIdx.y / hsplit, z = blockIdx.z;
+    const int per = H / G / hsplit;
+    const int h0 = g * (H / G) + (blockIdx.y % hsplit) * per;       // the block's first head
     const Sight s = sight_of(tok_pos[n0 + n], size, keep);
     const int c_lo = z * TV_PART, c_hi = min(s.n, c_lo + TV_PART);
     if (c_lo >= s.n) return;             // talk_parts_kernel reads only the parts a token has
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int* bt = table + (size_t)tok_seq[n0 + n] * table_stride;
-    const float* rows = W + ((size_t)n * H + (size_t)g * per) * row_stride;
+    const float* rows = W + ((size_t)n * H + h0) * row_stride;
     const int e0 = lane * E;
     const bool mine = e0 < dv;
     const bool whole = layout == LUMEN_LAYOUT_LINEAR && dv % E == 0;      // a lane's values move as one piece
@@ -371,7 +375,7 @@ talk_values_kernel(const float* __restrict__ W, int row_stride, const T* __restr
         float a = 0.0f;
 #pragma unroll
         for (int w8 = 0; w8 < TV_THREADS / 32; ++w8) a += acc_s[((size_t)w8 * per + hh) * width + e];
-        const int h = g * per + hh;
+        const int h = h0 + hh;
         if (parts) parts[(((size_t)z * n_rows + n) * H + h) * dv + e] = a;
         else out[((size_t)(n0 + n) * H + h) * dv + e] = from_f32<T>(a);
     }
@@ -380,10 +384,11 @@ talk_values_kernel(const float* __restrict__ W, int row_stride, const T* __restr
 template <typename T, int E>
 static void launch_values(int per, dim3 grid, size_t smem, cudaStream_t stream, const float* W, int row_stride,
                           const T* vc, const int* table, int table_stride, const int* tok_seq, const int* tok_pos,
-                          T* out, float* parts, int n0, int rows, int H, int G, int dv, int size, int keep, int layout) {
+                          T* out, float* parts, int n0, int rows, int H, int G, int dv, int size, int keep, int layout,
+                          int hsplit) {
 #define LUMEN_TV(PER_)                                                                                               \
     lumen_launch(talk_values_kernel<T, E, PER_>, grid, dim3(TV_THREADS), smem, stream, W, row_stride, vc, table,     \
-                 table_stride, tok_seq, tok_pos, out, parts, n0, rows, H, G, dv, size, keep, layout)
+                 table_stride, tok_seq, tok_pos, out, parts, n0, rows, H, G, dv, size, keep, layout, hsplit)
     if (per <= 1) LUMEN_TV(1);
     else if (per <= 2) LUMEN_TV(2);
     else if (per <= 4) LUMEN_TV(4);
@@ -699,7 +704,9 @@ static int attn_talk_run(const T* q, const T* kc, const T* vc, const int* table,
                          float* parts, int N,
                          int rows_per_pass, int row_stride, int H, int G, int d, int dv, int size, int keep,
                          float scale, int k_layout, int v_layout, cudaStream_t stream) {
-    const int per = H / G;
+    int hsplit = 1;                      // blocks a kv head's heads are dealt out over: shares of at most 16 heads
+    while ((H / G) % hsplit || (H / G) / hsplit > TS_MAX_PER) ++hsplit;
+    const int per = H / G / hsplit;
     const int chunks = (row_stride + TS_COLS - 1) / TS_COLS;
     const int Z = (row_stride + TV_PART - 1) / TV_PART;
     const size_t smem1 = (size_t)per * (d + TS_COLS) * sizeof(float);
@@ -711,18 +718,18 @@ static int attn_talk_run(const T* q, const T* kc, const T* vc, const int* table,
         cudaFuncSetAttribute(talk_scores_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem1);
     for (int n0 = 0; n0 < N; n0 += rows_per_pass) {
         const int rows = min(rows_per_pass, N - n0);
-        lumen_launch(talk_scores_kernel<T>, dim3(rows, G, chunks), dim3(TS_THREADS), smem1, stream, q, kc, table,
-                     table_stride, tok_seq, tok_pos, W, stats, row_stride, n0, H, G, d, size, keep, scale, k_layout);
+        lumen_launch(talk_scores_kernel<T>, dim3(rows, G * hsplit, chunks), dim3(TS_THREADS), smem1, stream, q, kc, table,
+                     table_stride, tok_seq, tok_pos, W, stats, row_stride, n0, H, G, d, size, keep, scale, k_layout, hsplit);
         launch_mix<false>(dim3(rows, (row_stride + TM_THREADS - 1) / TM_THREADS), stream, W, W2, (const float*)stats,
                           chunks, row_stride, tok_pos, n0, talk, H, size, keep);
         if (E == 4)
-            launch_values<T, 4>(per, dim3(rows, G, Z), smem3, stream, (const float*)W2, row_stride, vc, table,
+            launch_values<T, 4>(per, dim3(rows, G * hsplit, Z), smem3, stream, (const float*)W2, row_stride, vc, table,
                                 table_stride, tok_seq, tok_pos, out, Z > 1 ? parts : (float*)nullptr, n0, rows, H, G, dv,
-                                size, keep, v_layout);
+                                size, keep, v_layout, hsplit);
         else
-            launch_values<T, 8>(per, dim3(rows, G, Z), smem3, stream, (const float*)W2, row_stride, vc, table,
+            launch_values<T, 8>(per, dim3(rows, G * hsplit, Z), smem3, stream, (const float*)W2, row_stride, vc, table,
                                 table_stride, tok_seq, tok_pos, out, Z > 1 ? parts : (float*)nullptr, n0, rows, H, G, dv,
-                                size, keep, v_layout);
+                                size, keep, v_layout, hsplit);
         if (Z > 1) {
             const size_t total = (size_t)rows * H * dv;
             lumen_launch(talk_parts_kernel<T>, dim3((unsigned)((total + 255) / 256)), dim3(256), 0, stream,
@@ -740,7 +747,7 @@ LUMEN_API int lumen_attn_talk(const void* q, const void* kc, const void* vc, con
                               int dv, int size, int keep, float scale, int k_layout, int v_layout,
                               cudaStream_t stream) {
     if (N <= 0) return 0;
-    if (H <= 0 || G <= 0 || H % G || H / G > TS_MAX_PER || H > TM_MAX_H || d <= 0 || dv <= 0 || dv > 256 ||
+    if (H <= 0 || G <= 0 || H % G || H > TM_MAX_H || d <= 0 || dv <= 0 || dv > 256 ||
         rows_per_pass <= 0 || row_stride <= 0 || size < 0 || keep < 0 || H > 65535)
         return LUMEN_ERR_UNSUPPORTED;
     if ((row_stride + TS_COLS - 1) / TS_COLS > 65535) return LUMEN_ERR_UNSUPPORTED;

@@ -217,7 +217,8 @@ def run_mixer(mixer, rt, pieces):
 @pytest.mark.parametrize("dtype", [F32, BF16])
 @pytest.mark.parametrize("m", [attention(4, 2, 16, 24, 0.3, 9, 2), attention(6, 6, 32, 32, 0.11, 70, 0),
                                attention(3, 1, 32, 16, 0.2, 1000, 0), attention(2, 2, 64, 128, 0.15, 33, 70),
-                               attention(5, 5, 24, 8, 0.5, 1, 1)])
+                               attention(5, 5, 24, 8, 0.5, 1, 1), attention(34, 1, 20, 10, 0.4, 50, 3),
+                               attention(3, 3, 48, 80, 0.2, 70, 0)])
 def test_talking_attention_part(m, dtype):
     """The mixer alone: a whole sequence, then the same continued token by token."""
     D, T = 48, 150
