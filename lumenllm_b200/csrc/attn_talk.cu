@@ -8,11 +8,14 @@
 //
 // The mix needs every head's NORMALISED weights at a (query, key) pair, so the weights cannot
 // stay inside one head's running softmax as in flash attention. The work is cut into three
-// kernels around a float32 scratch matrix W[token][head][column]:
+// phases around a float32 scratch matrix W[token][head][column]:
 //   1. scores:  W = scale * q . k                       (per head, keys in parallel)
 //   2. softmax over a token's columns per head, then the mix over heads at every column
-//      (in place: W becomes m)
 //   3. values:  out_h = sum over columns of m_h * v     (per head, keys in parallel)
+// In steps of prompts (bfloat16) the three are three kernels, 1 and 3 on the tensor cores, 2 in
+// place (W becomes m). Otherwise 2 is done by the values kernel itself, for its own columns: the
+// scores kernel leaves every 64-column chunk's maximum and sum of exponentials, from which any
+// block has all heads' normalisers in a few loads.
 // Column c of a token stands for key c if c < kept, else key lo + (c - kept), with
 // lo = max(0, p - size + 1) and kept = min(keep, lo): the kept first keys, then the window.
 // A token has kept + p - lo + 1 columns; the matrix's row stride is the most any token of the
@@ -142,29 +145,24 @@ talk_scores_kernel(const T* __restrict__ q, const T* __restrict__ kcache, const 
     }
 }
 
-// ---------------------------------------------------------------- 2. softmax and mix
+// ---------------------------------------------------------------- 2. softmax and mix (prompt steps)
 // Block = token. First every head's maximum and sum over the token's columns (a warp a head),
-// then, 256 columns at a time: every head's weight at the column into shared memory, and from
-// there each output head's mix, written over the scores.
-#define TM_THREADS 256
-#define TM_MAX_H 128
-// With HALF (prompt steps of the bfloat16 path) exponentials are the fast form, as in the
-// library's other serving attention kernels, and the mixed weights are written as bfloat16
-// over the front half of each row (the tensor-core values kernel reads them so): column c then lands on the bytes of the float32
-// columns c / 2, which belong to this or an earlier group of 256 columns, all read before the
-// barrier.
-// Without HALF the mix goes to a matrix of its own (Wout), and the blocks (token, group of 256
-// columns) of a token each find the heads' maxima and sums for themselves: a step of single
-// tokens has too few tokens to fill the device with a block a token.
+// then, 256 columns at a time: every head's weight at the column, and from those each output
+// head's mix, written as bfloat16 over the front half of the head's float32 row (the tensor-core
+// values kernel reads them so): column c then lands on the bytes of the float32 columns c / 2,
+// which belong to this or an earlier group of 256 columns, all read before the barrier.
+// Exponentials are the fast form, as in the library's other serving attention kernels (this
+// kernel runs in bfloat16 prompt steps only; everywhere else the values kernel mixes, with expf).
 // HR > 0 (at least the number of heads, a multiple of 4): a thread keeps its column's weights of
 // all heads in registers and reads the talk matrix four values at a time; HR = 0: any number of
 // heads, the weights go through shared memory.
-template <bool HALF, int HR>
+#define TM_THREADS 256
+#define TM_MAX_H 128
+template <int HR>
 __global__ void __launch_bounds__(TM_THREADS)
-talk_softmax_mix_kernel(float* __restrict__ W, float* __restrict__ Wout, const float* __restrict__ stats, int chunks,
-                        int row_stride, const int* __restrict__ tok_pos, int n0, const float* __restrict__ talk, int H,
-                        int size, int keep) {
-    extern __shared__ __align__(16) float sm[];   // H * H (talk) + H * TM_THREADS (weights)
+talk_softmax_mix_kernel(float* __restrict__ W, int row_stride, const int* __restrict__ tok_pos, int n0,
+                        const float* __restrict__ talk, int H, int size, int keep) {
+    extern __shared__ __align__(16) float sm[];   // the talk matrix; with HR = 0 also H * TM_THREADS weights
     __shared__ float mx[TM_MAX_H], inv[TM_MAX_H];
     float* tk = sm;
     float* ws = sm + H * H;                   // used with HR = 0 only
@@ -177,57 +175,37 @@ talk_softmax_mix_kernel(float* __restrict__ W, float* __restrict__ Wout, const f
     pdl_wait();
     const int n = blockIdx.x;
     const Sight s = sight_of(tok_pos[n0 + n], size, keep);
-    if (!HALF && (int)blockIdx.y * TM_THREADS >= s.n) return;
     float* rows = W + (size_t)n * H * row_stride;
-    float* rows_out = Wout + (size_t)n * H * row_stride;
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     for (int g = warp; g < H; g += TM_THREADS / 32) {
         const float* row = rows + (size_t)g * row_stride;
         float m = -INFINITY, l = 0.0f;
-        if (!HALF && stats) {
-            // per chunk of 64 columns the scores kernel left (maximum, sum of exponentials)
-            const float* st = stats + ((size_t)n * H + g) * chunks * 2;
-            const int used = (s.n + TS_COLS - 1) / TS_COLS;
-            for (int c = lane; c < used; c += 32) m = fmaxf(m, st[2 * c]);
-            m = warp_max(m);
-            for (int c = lane; c < used; c += 32) l += st[2 * c + 1] * expf(st[2 * c] - m);
-            l = warp_sum(l);
-        } else {
-            for (int c = lane; c < s.n; c += 32) m = fmaxf(m, row[c]);
-            m = warp_max(m);
-            for (int c = lane; c < s.n; c += 32) l += HALF ? __expf(row[c] - m) : expf(row[c] - m);
-            l = warp_sum(l);
-        }
+        for (int c = lane; c < s.n; c += 32) m = fmaxf(m, row[c]);
+        m = warp_max(m);
+        for (int c = lane; c < s.n; c += 32) l += __expf(row[c] - m);
+        l = warp_sum(l);
         if (lane == 0) {
             mx[g] = m;
             inv[g] = 1.0f / l;
         }
     }
     __syncthreads();
-    const int c_begin = HALF ? 0 : (int)blockIdx.y * TM_THREADS, c_end = HALF ? s.n : min(s.n, c_begin + TM_THREADS);
-    for (int c0 = c_begin; c0 < c_end; c0 += TM_THREADS) {
+    for (int c0 = 0; c0 < s.n; c0 += TM_THREADS) {
         const int c = c0 + threadIdx.x;
         float p[HR > 0 ? HR : 1];
         if (c < s.n) {
             if (HR > 0) {
 #pragma unroll
-                for (int g = 0; g < HR; ++g) {
-                    const float x = g < H ? rows[(size_t)g * row_stride + c] - mx[g] : 0.0f;
-                    p[g] = g < H ? (HALF ? __expf(x) : expf(x)) * inv[g] : 0.0f;
-                }
+                for (int g = 0; g < HR; ++g)
+                    p[g] = g < H ? __expf(rows[(size_t)g * row_stride + c] - mx[g]) * inv[g] : 0.0f;
             } else {
-                for (int g = 0; g < H; ++g) {
-                    const float x = rows[(size_t)g * row_stride + c] - mx[g];
-                    ws[g * TM_THREADS + threadIdx.x] = (HALF ? __expf(x) : expf(x)) * inv[g];
-                }
+                for (int g = 0; g < H; ++g)
+                    ws[g * TM_THREADS + threadIdx.x] = __expf(rows[(size_t)g * row_stride + c] - mx[g]) * inv[g];
             }
         }
-        // a thread reads back only what it wrote itself; the barrier is for the narrow form,
-        // whose stores land on other threads' scores
-        if (HALF) __syncthreads();
+        __syncthreads();             // the narrow stores below land on other threads' scores
         if (c < s.n)
             for (int h = 0; h < H; ++h) {
-                const float* t = tk + h * H;
                 float a = 0.0f;
                 if (HR > 0) {
                     // the talk matrix lies in rows of HR values (zeros behind the heads)
@@ -241,25 +219,22 @@ talk_softmax_mix_kernel(float* __restrict__ W, float* __restrict__ Wout, const f
                         a = fmaf(w.w, p[4 * g4 + 3], a);
                     }
                 } else {
+                    const float* t = tk + h * H;
                     for (int g = 0; g < H; ++g) a = fmaf(t[g], ws[g * TM_THREADS + threadIdx.x], a);
                 }
-                if (HALF) reinterpret_cast<__nv_bfloat16*>(rows + (size_t)h * row_stride)[c] = __float2bfloat16_rn(a);
-                else rows_out[(size_t)h * row_stride + c] = a;
+                reinterpret_cast<__nv_bfloat16*>(rows + (size_t)h * row_stride)[c] = __float2bfloat16_rn(a);
             }
-        if (HALF) __syncthreads();
     }
 }
 
-template <bool HALF>
-static void launch_mix(dim3 grid, cudaStream_t stream, float* W, float* Wout, const float* stats, int chunks,
-                       int row_stride, const int* tok_pos, int n0, const float* talk, int H, int size, int keep) {
+static void launch_mix(int n_rows, cudaStream_t stream, float* W, int row_stride, const int* tok_pos, int n0,
+                       const float* talk, int H, int size, int keep) {
 #define LUMEN_MIX(HR_, SMEM_)                                                                                          \
     do {                                                                                                               \
-        auto k = talk_softmax_mix_kernel<HALF, HR_>;                                                                   \
+        auto k = talk_softmax_mix_kernel<HR_>;                                                                         \
         const size_t smem = (SMEM_);                                                                                   \
         if (smem > 40 * 1024) cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);         \
-        lumen_launch(k, grid, dim3(TM_THREADS), smem, stream, W, Wout, stats, chunks, row_stride, tok_pos, n0, talk, H, \
-                     size, keep);                                                                                      \
+        lumen_launch(k, dim3(n_rows), dim3(TM_THREADS), smem, stream, W, row_stride, tok_pos, n0, talk, H, size, keep); \
     } while (0)
     if (H <= 8) LUMEN_MIX(8, (size_t)H * 8 * sizeof(float));
     else if (H <= 16) LUMEN_MIX(16, (size_t)H * 16 * sizeof(float));
@@ -297,12 +272,21 @@ __device__ __forceinline__ void load_vals<float, 4>(const float* p, float* v) {
 
 template <typename T, int E, int PER>
 __global__ void __launch_bounds__(TV_THREADS)
-talk_values_kernel(const float* __restrict__ W, int row_stride, const T* __restrict__ vcache,
+talk_values_kernel(const float* __restrict__ W, const float* __restrict__ stats, int chunks,
+                   const float* __restrict__ talk, int row_stride, const T* __restrict__ vcache,
                    const int* __restrict__ table, int table_stride, const int* __restrict__ tok_seq,
                    const int* __restrict__ tok_pos, T* __restrict__ out, float* __restrict__ parts, int n0, int n_rows,
                    int H, int G, int dv, int size, int keep, int layout, int hsplit) {
-    extern __shared__ __align__(16) float acc_s[];      // [warps][per][32 * E]
+    // [warps][per][32 * E] sums | [2][per][TV_PART] mixed weights | [per][H] talk rows | [H] maxima | [H] 1 / sums
+    extern __shared__ __align__(16) float acc_s[];
     pdl_trigger();       // the kernel behind may come to rest and wait; it still waits for this one's end
+    // the talk matrix never changes: the rows of the block's heads are fetched before the wait
+    {
+        const int per_ = H / G / hsplit;
+        const int h0_ = (blockIdx.y / hsplit) * (H / G) + (blockIdx.y % hsplit) * per_;
+        float* tkr_ = acc_s + (TV_THREADS / 32) * per_ * 32 * E + 2 * per_ * TV_PART;
+        for (int i = threadIdx.x; i < per_ * H; i += TV_THREADS) tkr_[i] = talk[(size_t)h0_ * H + i];
+    }
     pdl_wait();
     const int n = blockIdx.x, g = blockIdx.y / hsplit, z = blockIdx.z;
     const int per = H / G / hsplit;
@@ -312,7 +296,62 @@ talk_values_kernel(const float* __restrict__ W, int row_stride, const T* __restr
     if (c_lo >= s.n) return;             // talk_parts_kernel reads only the parts a token has
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int* bt = table + (size_t)tok_seq[n0 + n] * table_stride;
-    const float* rows = W + ((size_t)n * H + h0) * row_stride;
+    // the pages and rows of the warp's columns are asked for now and used behind the mix
+    constexpr int COLS = TV_PART / (TV_THREADS / 32);
+    int my_page = 0, my_r = 0;
+    {
+        const int c = c_lo + warp + (TV_THREADS / 32) * lane;
+        if (lane < COLS && c < c_hi) {
+            const int j = key_of(s, c);
+            my_page = bt[j / LUMEN_PAGE];
+            my_r = j % LUMEN_PAGE;
+        }
+    }
+    // Softmax and mix for the block's own columns (W holds the scores of ALL heads; the scores
+    // kernel left every 64-column chunk's maximum and sum of exponentials in `stats`): first each
+    // head's maximum and sum over the token's columns, then at each of the block's columns every
+    // head's weight and, from those, the mix for the block's heads, into shared memory.
+    float* wmix = acc_s + (TV_THREADS / 32) * per * 32 * E;
+    const float* tkr = wmix + 2 * per * TV_PART;
+    float* mx = wmix + 2 * per * TV_PART + per * H;
+    float* inv = mx + H;
+    for (int g2 = warp; g2 < H; g2 += TV_THREADS / 32) {
+        const float* st = stats + ((size_t)n * H + g2) * chunks * 2;
+        const int used = (s.n + TS_COLS - 1) / TS_COLS;
+        float m = -INFINITY, l = 0.0f;
+        for (int c = lane; c < used; c += 32) m = fmaxf(m, st[2 * c]);
+        m = warp_max(m);
+        for (int c = lane; c < used; c += 32) l += st[2 * c + 1] * expf(st[2 * c] - m);
+        l = warp_sum(l);
+        if (lane == 0) {
+            mx[g2] = m;
+            inv[g2] = 1.0f / l;
+        }
+    }
+    __syncthreads();
+    {
+        // thread t: column t % TV_PART; the two halves of the block share the heads whose weights
+        // enter the mix (each half its own sum, added when the weights are taken below)
+        const int cc = threadIdx.x % TV_PART, c = c_lo + cc, half = threadIdx.x / TV_PART;
+        constexpr int HALVES = TV_THREADS / TV_PART;
+        const int share = (H + HALVES - 1) / HALVES, g_lo = half * share, g_hi = min(H, g_lo + share);
+        if (c < c_hi) {
+            float a[PER];
+#pragma unroll
+            for (int hh = 0; hh < PER; ++hh) a[hh] = 0.0f;
+            const float* col = W + (size_t)n * H * row_stride + c;
+            for (int g2 = g_lo; g2 < g_hi; ++g2) {
+                const float pw = expf(col[(size_t)g2 * row_stride] - mx[g2]) * inv[g2];
+#pragma unroll
+                for (int hh = 0; hh < PER; ++hh)
+                    if (hh < per) a[hh] = fmaf(tkr[hh * H + g2], pw, a[hh]);
+            }
+#pragma unroll
+            for (int hh = 0; hh < PER; ++hh)
+                if (hh < per) wmix[(half * per + hh) * TV_PART + cc] = a[hh];
+        }
+    }
+    __syncthreads();
     const int e0 = lane * E;
     const bool mine = e0 < dv;
     const bool whole = layout == LUMEN_LAYOUT_LINEAR && dv % E == 0;      // a lane's values move as one piece
@@ -323,20 +362,15 @@ talk_values_kernel(const float* __restrict__ W, int row_stride, const T* __restr
         for (int k = 0; k < E; ++k) acc[hh][k] = 0.0f;
     // Lane l fetches, for the warp's l-th column, the page and row of its key and the heads'
     // weights; the walk below takes them from there, so that no load in it waits for another.
-    constexpr int COLS = TV_PART / (TV_THREADS / 32);
-    int my_page = 0, my_r = 0;
     float my_w[PER];
 #pragma unroll
     for (int hh = 0; hh < PER; ++hh) my_w[hh] = 0.0f;
     {
         const int c = c_lo + warp + (TV_THREADS / 32) * lane;
         if (lane < COLS && c < c_hi) {
-            const int j = key_of(s, c);
-            my_page = bt[j / LUMEN_PAGE];
-            my_r = j % LUMEN_PAGE;
 #pragma unroll
             for (int hh = 0; hh < PER; ++hh)
-                if (hh < per) my_w[hh] = rows[(size_t)hh * row_stride + c];
+                if (hh < per) my_w[hh] = wmix[hh * TV_PART + (c - c_lo)] + wmix[(per + hh) * TV_PART + (c - c_lo)];
         }
     }
 #pragma unroll 4
@@ -382,12 +416,13 @@ talk_values_kernel(const float* __restrict__ W, int row_stride, const T* __restr
 }
 
 template <typename T, int E>
-static void launch_values(int per, dim3 grid, size_t smem, cudaStream_t stream, const float* W, int row_stride,
-                          const T* vc, const int* table, int table_stride, const int* tok_seq, const int* tok_pos,
+static void launch_values(int per, dim3 grid, size_t smem, cudaStream_t stream, const float* W, const float* stats,
+                          int chunks, const float* talk, int row_stride, const T* vc, const int* table, int table_stride, const int* tok_seq, const int* tok_pos,
                           T* out, float* parts, int n0, int rows, int H, int G, int dv, int size, int keep, int layout,
                           int hsplit) {
 #define LUMEN_TV(PER_)                                                                                               \
-    lumen_launch(talk_values_kernel<T, E, PER_>, grid, dim3(TV_THREADS), smem, stream, W, row_stride, vc, table,     \
+    lumen_launch(talk_values_kernel<T, E, PER_>, grid, dim3(TV_THREADS), smem, stream, W, stats, chunks, talk,       \
+                 row_stride, vc, table,                                                                              \
                  table_stride, tok_seq, tok_pos, out, parts, n0, rows, H, G, dv, size, keep, layout, hsplit)
     if (per <= 1) LUMEN_TV(1);
     else if (per <= 2) LUMEN_TV(2);
@@ -677,7 +712,7 @@ LUMEN_API int lumen_attn_talk_prompt(const void* q, const void* kc, const void* 
         lumen_launch(talk_scores_mma_kernel, grid1, dim3(TP_THREADS), smem1, stream, (const __nv_bfloat16*)q,
                      (const __nv_bfloat16*)kc, table, table_stride, cu_q, seq_start, B, W, row_stride, n0, rows, H, G, d,
                      size, keep, scale);
-        launch_mix<true>(dim3(rows), stream, W, W, (const float*)nullptr, 0, row_stride, tok_pos, n0, talk, H, size, keep);
+        launch_mix(rows, stream, W, row_stride, tok_pos, n0, talk, H, size, keep);
 #define LUMEN_TALK_VALUES(NT_)                                                                                        \
     case NT_:                                                                                                         \
         launch_values_mma<NT_>(grid, stream, (const float*)W, row_stride, (const __nv_bfloat16*)vc, table,            \
@@ -696,38 +731,43 @@ LUMEN_API int lumen_attn_talk_prompt(const void* q, const void* kc, const void* 
 }
 
 // ---------------------------------------------------------------- host side
-// q [N, H, d], out [N, H, dv]; scratch: W (scores) and W2 (mixed weights), each float32
-// [rows, H, row_stride] with rows >= min(N, rows_per_pass); parts: float32 [Z, rows, H, dv] when row_stride > TV_PART (Z parts), else null.
+// q [N, H, d], out [N, H, dv]; scratch: W (scores) float32 [rows, H, row_stride] and stats float32
+// [rows, H, chunks of 64 columns, 2] with rows >= min(N, rows_per_pass); parts: float32 [Z, rows, H, dv] when row_stride > TV_PART (Z parts), else null.
 template <typename T>
 static int attn_talk_run(const T* q, const T* kc, const T* vc, const int* table, int table_stride, const int* tok_seq,
-                         const int* tok_pos, const float* talk, T* out, float* W, float* W2, float* stats,
+                         const int* tok_pos, const float* talk, T* out, float* W, float* stats,
                          float* parts, int N,
                          int rows_per_pass, int row_stride, int H, int G, int d, int dv, int size, int keep,
                          float scale, int k_layout, int v_layout, cudaStream_t stream) {
-    int hsplit = 1;                      // blocks a kv head's heads are dealt out over: shares of at most 16 heads
-    while ((H / G) % hsplit || (H / G) / hsplit > TS_MAX_PER) ++hsplit;
+    // blocks a kv head's heads are dealt out over: equal shares of at most 16 heads whose sums and
+    // mixed weights fit the values kernel's shared memory
+    const int E = (dv <= 128 && dv % 4 == 0) ? 4 : 8;
+    auto values_smem = [&](int per_) {
+        return ((size_t)(TV_THREADS / 32) * per_ * 32 * E + (size_t)2 * per_ * TV_PART + (size_t)per_ * H + 2 * H) * sizeof(float);
+    };
+    int hsplit = 1;
+    while ((H / G) % hsplit || (H / G) / hsplit > TS_MAX_PER || (values_smem((H / G) / hsplit) > 48 * 1024 && hsplit < H / G))
+        ++hsplit;
     const int per = H / G / hsplit;
     const int chunks = (row_stride + TS_COLS - 1) / TS_COLS;
     const int Z = (row_stride + TV_PART - 1) / TV_PART;
     const size_t smem1 = (size_t)per * (d + TS_COLS) * sizeof(float);
-    const size_t smem2 = ((size_t)H * H + (size_t)H * TM_THREADS) * sizeof(float);
-    const int E = (dv <= 128 && dv % 4 == 0) ? 4 : 8;
-    const size_t smem3 = (size_t)(TV_THREADS / 32) * per * 32 * E * sizeof(float);
-    if (smem1 > 160 * 1024 || smem2 > 200 * 1024 || smem3 > 48 * 1024) return LUMEN_ERR_UNSUPPORTED;
+    const size_t smem3 = values_smem(per);
+    if (smem1 > 160 * 1024 || smem3 > 48 * 1024) return LUMEN_ERR_UNSUPPORTED;
     if (smem1 > 40 * 1024)
         cudaFuncSetAttribute(talk_scores_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem1);
     for (int n0 = 0; n0 < N; n0 += rows_per_pass) {
         const int rows = min(rows_per_pass, N - n0);
         lumen_launch(talk_scores_kernel<T>, dim3(rows, G * hsplit, chunks), dim3(TS_THREADS), smem1, stream, q, kc, table,
                      table_stride, tok_seq, tok_pos, W, stats, row_stride, n0, H, G, d, size, keep, scale, k_layout, hsplit);
-        launch_mix<false>(dim3(rows, (row_stride + TM_THREADS - 1) / TM_THREADS), stream, W, W2, (const float*)stats,
-                          chunks, row_stride, tok_pos, n0, talk, H, size, keep);
         if (E == 4)
-            launch_values<T, 4>(per, dim3(rows, G * hsplit, Z), smem3, stream, (const float*)W2, row_stride, vc, table,
+            launch_values<T, 4>(per, dim3(rows, G * hsplit, Z), smem3, stream, (const float*)W, (const float*)stats,
+                                chunks, talk, row_stride, vc, table,
                                 table_stride, tok_seq, tok_pos, out, Z > 1 ? parts : (float*)nullptr, n0, rows, H, G, dv,
                                 size, keep, v_layout, hsplit);
         else
-            launch_values<T, 8>(per, dim3(rows, G * hsplit, Z), smem3, stream, (const float*)W2, row_stride, vc, table,
+            launch_values<T, 8>(per, dim3(rows, G * hsplit, Z), smem3, stream, (const float*)W, (const float*)stats,
+                                chunks, talk, row_stride, vc, table,
                                 table_stride, tok_seq, tok_pos, out, Z > 1 ? parts : (float*)nullptr, n0, rows, H, G, dv,
                                 size, keep, v_layout, hsplit);
         if (Z > 1) {
@@ -743,7 +783,7 @@ static int attn_talk_run(const T* q, const T* kc, const T* vc, const int* table,
 
 LUMEN_API int lumen_attn_talk(const void* q, const void* kc, const void* vc, const int* table, int table_stride,
                               const int* tok_seq, const int* tok_pos, const float* talk, void* out, float* W,
-                              float* W2, float* stats, float* parts, int is_bf16, int N, int rows_per_pass, int row_stride, int H, int G, int d,
+                              float* stats, float* parts, int is_bf16, int N, int rows_per_pass, int row_stride, int H, int G, int d,
                               int dv, int size, int keep, float scale, int k_layout, int v_layout,
                               cudaStream_t stream) {
     if (N <= 0) return 0;
@@ -753,13 +793,13 @@ LUMEN_API int lumen_attn_talk(const void* q, const void* kc, const void* vc, con
     if ((row_stride + TS_COLS - 1) / TS_COLS > 65535) return LUMEN_ERR_UNSUPPORTED;
     if ((k_layout == LUMEN_LAYOUT_SW128 && (!is_bf16 || d % 64)) || (v_layout == LUMEN_LAYOUT_SW128 && (!is_bf16 || dv % 64)))
         return LUMEN_ERR_UNSUPPORTED;
-    if ((row_stride > TV_PART && !parts) || !W || !W2 || W == W2 || !stats) return LUMEN_ERR_BAD_ARGUMENT;
+    if ((row_stride > TV_PART && !parts) || !W || !stats) return LUMEN_ERR_BAD_ARGUMENT;
     if (is_bf16)
         return attn_talk_run<__nv_bfloat16>((const __nv_bfloat16*)q, (const __nv_bfloat16*)kc, (const __nv_bfloat16*)vc,
-                                            table, table_stride, tok_seq, tok_pos, talk, (__nv_bfloat16*)out, W, W2, stats, parts, N,
+                                            table, table_stride, tok_seq, tok_pos, talk, (__nv_bfloat16*)out, W, stats, parts, N,
                                             rows_per_pass, row_stride, H, G, d, dv, size, keep, scale, k_layout,
                                             v_layout, stream);
     return attn_talk_run<float>((const float*)q, (const float*)kc, (const float*)vc, table, table_stride, tok_seq,
-                                tok_pos, talk, (float*)out, W, W2, stats, parts, N, rows_per_pass, row_stride, H, G, d, dv, size,
+                                tok_pos, talk, (float*)out, W, stats, parts, N, rows_per_pass, row_stride, H, G, d, dv, size,
                                 keep, scale, k_layout, v_layout, stream);
 }

@@ -273,17 +273,17 @@ def attn_talk(q, kcache, vcache, block_table, tok_seq, tok_pos, talk, window, ke
                 row_stride, nq, nkv, d, dv, int(window), int(keep_first), float(scale), stream_ptr()),
               "attn_talk_prompt")
         return out
-    rows_per_pass = max(1, min(N, ATTN_TALK_SCRATCH_BYTES // (2 * nq * row_stride * 4)))
-    W = torch.empty((2, rows_per_pass, nq, row_stride), dtype=F32, device=q.device)   # scores, mixed weights
+    rows_per_pass = max(1, min(N, ATTN_TALK_SCRATCH_BYTES // (nq * row_stride * 4)))
+    W = torch.empty((rows_per_pass, nq, row_stride), dtype=F32, device=q.device)      # the scores
     chunks = -(-row_stride // 64)             # per 64 columns the scores kernel leaves (maximum, sum)
     stats = torch.empty((rows_per_pass, nq, chunks, 2), dtype=F32, device=q.device)
     Z = -(-row_stride // ATTN_TALK_PART)
     parts = torch.empty((Z, rows_per_pass, nq, dv), dtype=F32, device=q.device) if Z > 1 else None
     f = fn("attn_talk", "lumen_attn_talk",
-           [P, P, P, P, c_int, P, P, P, P, P, P, P, P, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
+           [P, P, P, P, c_int, P, P, P, P, P, P, P, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
             c_int, c_float, c_int, c_int, P])
     check(f(ptr(q), ptr(kcache), ptr(vcache), ptr(block_table), block_table.stride(0), ptr(tok_seq), ptr(tok_pos),
-            ptr(talk), ptr(out), ptr(W[0]), ptr(W[1]), ptr(stats), ptr(parts), _is_bf16(q), N, rows_per_pass, row_stride, nq, nkv, d, dv,
+            ptr(talk), ptr(out), ptr(W), ptr(stats), ptr(parts), _is_bf16(q), N, rows_per_pass, row_stride, nq, nkv, d, dv,
             int(window), int(keep_first), float(scale), int(k_layout), int(v_layout), stream_ptr()), "attn_talk")
     return out
 
