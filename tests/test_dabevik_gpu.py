@@ -229,6 +229,23 @@ def test_talking_attention_part(m, dtype):
     close(got, ref, dtype)
 
 
+@pytest.mark.parametrize("dtype", [F32, BF16])
+def test_attention_in_passes_over_a_steps_rows(dtype, monkeypatch):
+    """A step whose weights matrix would not fit its scratch is worked on in passes over its rows
+    (here the scratch is made tiny: 64 rows a pass on the tensor cores, 7 in the general kernels);
+    sequences and their 64-query tiles lie across the passes' borders."""
+    from lumenllm_b200.ops import kernels as K
+    m = attention(4, 2, 32, 32, 0.2, 90, 3)
+    D = 48
+    mixer, w = attention_part(m, D, dtype, seed=11)
+    monkeypatch.setattr(K, "ATTN_TALK_PROMPT_SCRATCH_BYTES", 1)
+    monkeypatch.setattr(K, "ATTN_TALK_SCRATCH_BYTES", 7 * 4 * 93 * 4)
+    y = torch.randn(333, D, generator=torch.Generator().manual_seed(12)).to(dtype).float()
+    ref = P.talking_attention(y, w, "l0.mix.", m, 1e-6)
+    got = run_mixer(mixer, runtime(dtype), [y[:150], y[150:331], y[331:332], y[332:]])
+    close(got, ref, dtype)
+
+
 @pytest.mark.parametrize("decode", [False, True])
 @pytest.mark.parametrize("dtype", [F32, BF16])
 def test_one_loud_key_at_every_edge_of_sight(dtype, decode):
