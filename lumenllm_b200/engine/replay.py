@@ -31,7 +31,7 @@ def main(argv=None) -> int:
     ap.add_argument("--dtype", required=True, choices=["bfloat16", "float32"])
     ap.add_argument("--out", required=True, help="folder that receives <step>.f32")
     ap.add_argument("--max-tokens", type=int, required=True,
-                    help="most tokens live requests hold at any time (each rounded up to 64)")
+                    help="most tokens live requests hold at any time")
     args = ap.parse_args(argv)
 
     from .engine import Engine, StepEntry
@@ -39,7 +39,11 @@ def main(argv=None) -> int:
     out.mkdir(parents=True, exist_ok=True)
     # tensors that no part of the model reads are reported, not refused: a replay is about the
     # tensors that are read
-    engine = Engine.from_folder(args.model, dtype=args.dtype, max_tokens=args.max_tokens, strict_weights=False)
+    # --max-tokens counts tokens, the cache hands out pages: a live request's last page is part
+    # empty, so room for one more page for each of up to 64 live requests is added
+    from ..cache.kv import PAGE
+    engine = Engine.from_folder(args.model, dtype=args.dtype, max_tokens=args.max_tokens + 64 * PAGE,
+                                strict_weights=False)
     slots = {}
     for line in sys.stdin:
         line = line.strip()
