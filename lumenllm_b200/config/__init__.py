@@ -3,8 +3,9 @@ from .registry import (config_class_for, config_from_dict, known_architectures, 
                        register_architecture)
 from .qwen3 import Qwen3Config
 from .dabevik import DabevikConfig
+from .rasezen import RasezenConfig
 from .params import ParametersFile, SamplingDefaults
 
-__all__ = ["ConfigError", "LayerSpec", "ModelSpec", "PartSpec", "ScheduleEntry", "Qwen3Config", "DabevikConfig",
+__all__ = ["ConfigError", "LayerSpec", "ModelSpec", "PartSpec", "ScheduleEntry", "Qwen3Config", "DabevikConfig", "RasezenConfig",
            "config_class_for", "config_from_dict", "known_architectures", "load_config",
            "register_architecture", "ParametersFile", "SamplingDefaults"]

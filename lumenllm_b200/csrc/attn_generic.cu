@@ -1,7 +1,7 @@
 // General causal attention over the paged cache, for any number of new tokens
-// per sequence (whole prompts and single decoded tokens alike), any head size
-// that is a multiple of 16 up to 256, any number of heads and groups, with an
-// optional window. All arithmetic is float32 with the precise expf. It is the
+// per sequence (whole prompts and single decoded tokens alike), any key size and
+// any value size up to 256 (the two may differ), any number of heads and groups,
+// with an optional window. All arithmetic is float32 with the precise expf. It is the
 // attention of the 32-bit path and the plain device reference of the faster
 // bfloat16 kernels.
 //
@@ -19,8 +19,8 @@ __global__ void __launch_bounds__(AG_THREADS)
 attn_generic_kernel(const T* __restrict__ q, const T* __restrict__ kcache, const T* __restrict__ vcache,
                     const int* __restrict__ block_table, int bt_stride,
                     const int* __restrict__ tok_seq, const int* __restrict__ tok_pos,
-                    T* __restrict__ out, int nq, int nkv, int d, int window, float scale,
-                    int layout) {
+                    T* __restrict__ out, int nq, int nkv, int d, int dv, int window, float scale,
+                    int layout, int v_layout) {
     pdl_wait();      // nothing of this kernel touches global memory before this
     pdl_trigger();
     __shared__ float qs[AG_MAX_D];
@@ -65,41 +65,43 @@ attn_generic_kernel(const T* __restrict__ q, const T* __restrict__ kcache, const
         const int jbeg = max(c * AG_THREADS, lo), jend = min(c * AG_THREADS + AG_THREADS - 1, p);
         for (int jj = jbeg; jj <= jend; ++jj) {
             const int page = bt[jj / LUMEN_PAGE];
-            const T* vtile = vcache + ((size_t)page * nkv + kvh) * LUMEN_PAGE * d;
+            const T* vtile = vcache + ((size_t)page * nkv + kvh) * LUMEN_PAGE * dv;
             const int r = jj % LUMEN_PAGE;
             const float w = ps[jj - c * AG_THREADS];
-            if (tid < d) acc0 = fmaf(w, to_f32(vtile[tile_offset(layout, r, tid, d)]), acc0);
-            if (tid + AG_THREADS < d)
-                acc1 = fmaf(w, to_f32(vtile[tile_offset(layout, r, tid + AG_THREADS, d)]), acc1);
+            if (tid < dv) acc0 = fmaf(w, to_f32(vtile[tile_offset(v_layout, r, tid, dv)]), acc0);
+            if (tid + AG_THREADS < dv)
+                acc1 = fmaf(w, to_f32(vtile[tile_offset(v_layout, r, tid + AG_THREADS, dv)]), acc1);
         }
         m = m_new;
         __syncthreads();
     }
-    T* orow = out + ((size_t)n * nq + head) * d;
+    T* orow = out + ((size_t)n * nq + head) * dv;
     const float inv = 1.0f / l;
-    if (tid < d) orow[tid] = from_f32<T>(acc0 * inv);
-    if (tid + AG_THREADS < d) orow[tid + AG_THREADS] = from_f32<T>(acc1 * inv);
+    if (tid < dv) orow[tid] = from_f32<T>(acc0 * inv);
+    if (tid + AG_THREADS < dv) orow[tid + AG_THREADS] = from_f32<T>(acc1 * inv);
 }
 
 LUMEN_API int lumen_attn_generic(const void* q, const void* kcache, const void* vcache,
                                  const int* block_table, int bt_stride, const int* tok_seq,
                                  const int* tok_pos, void* out, int is_bf16, int N, int nq, int nkv,
-                                 int d, int window, float scale, int layout, cudaStream_t stream) {
+                                 int d, int dv, int window, float scale, int layout, int v_layout,
+                                 cudaStream_t stream) {
     if (N <= 0) return 0;
-    if (d <= 0 || d > AG_MAX_D || nq <= 0 || nkv <= 0 || nq % nkv != 0 || window < 0)
+    if (d <= 0 || d > AG_MAX_D || dv <= 0 || dv > AG_MAX_D || nq <= 0 || nkv <= 0 || nq % nkv != 0 || window < 0)
         return LUMEN_ERR_UNSUPPORTED;
     if (nq > 65535) return LUMEN_ERR_UNSUPPORTED;
     if (layout == LUMEN_LAYOUT_SW128 && (!is_bf16 || d % 64 != 0)) return LUMEN_ERR_UNSUPPORTED;
+    if (v_layout == LUMEN_LAYOUT_SW128 && (!is_bf16 || dv % 64 != 0)) return LUMEN_ERR_UNSUPPORTED;
     dim3 grid(N, nq);
     if (is_bf16)
         lumen_launch(attn_generic_kernel<__nv_bfloat16>, dim3(grid), dim3(AG_THREADS), 0, stream, 
             (const __nv_bfloat16*)q, (const __nv_bfloat16*)kcache, (const __nv_bfloat16*)vcache,
-            block_table, bt_stride, tok_seq, tok_pos, (__nv_bfloat16*)out, nq, nkv, d, window, scale,
-            layout);
+            block_table, bt_stride, tok_seq, tok_pos, (__nv_bfloat16*)out, nq, nkv, d, dv, window, scale,
+            layout, v_layout);
     else
         lumen_launch(attn_generic_kernel<float>, dim3(grid), dim3(AG_THREADS), 0, stream, 
             (const float*)q, (const float*)kcache, (const float*)vcache, block_table, bt_stride,
-            tok_seq, tok_pos, (float*)out, nq, nkv, d, window, scale, layout);
+            tok_seq, tok_pos, (float*)out, nq, nkv, d, dv, window, scale, layout, v_layout);
     LUMEN_LAUNCH_CHECK();
     return 0;
 }

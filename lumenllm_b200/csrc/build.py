@@ -32,6 +32,8 @@ MODULES = {
     "attn_generic": (["attn_generic.cu"], ["common.cuh"]),
     "layer_ops": (["layer_ops.cu"], ["common.cuh"]),
     "attn_talk": (["attn_talk.cu"], ["common.cuh", "mma_utils.cuh"]),
+    "ssm": (["ssm.cu"], ["common.cuh"]),
+    "moe": (["moe.cu"], ["common.cuh"]),
     "sample": (["sample.cu"], ["common.cuh"]),
     "attn_decode": (["attn_decode.cu"], ["common.cuh", "mma_utils.cuh", "qk_head.cuh", "attn_decode_noalloc.h"]),
     "attn_prefill": (["attn_prefill.cu"], ["common.cuh", "mma_utils.cuh"]),

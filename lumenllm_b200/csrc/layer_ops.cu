@@ -519,7 +519,11 @@ LUMEN_API int lumen_polynorm(const float* z, int n_split, long long split_stride
 // A row of the stacked projection holds Wq query values, Wk key values and Wv value values.
 // x = sum of the partials + bias; the query part is divided by its root mean square over ALL
 // Wq values (all heads at once) and multiplied by qw [Wq], the key part likewise with kw [Wk]
-// (a null weight leaves the part as it is); q goes out as [N, Wq], the key and the value of
+// (a null weight leaves the part as it is). Then, optionally, every query and key head is
+// rotated: with cs (cos, sin) [N, rot/2, 2], value i < rot/2 of a head is paired with value
+// i + rot/2, (u, v) -> (u cos - v sin, v cos + u sin), the head's other values pass. And,
+// optionally (v_unit), every value head is divided by its own root mean square over its dv
+// values (eps_v inside the root, no weight). q goes out as [N, Wq], the key and the value of
 // the token to its place in the paged cache: key tiles [page][kv head][PAGE][d], value tiles
 // [page][kv head][PAGE][dv].
 template <typename T, int V>
@@ -529,8 +533,8 @@ qkv_bias_norm_store_kernel(const float* __restrict__ qkv, int S, size_t split_st
                            const int* __restrict__ cache_pos, const int* __restrict__ tok_seq,
                            const int* __restrict__ table, int table_stride, T* __restrict__ q_out,
                            T* __restrict__ kc, T* __restrict__ vc, int Wq, int Wk, int Wv, int G, int d, int dv,
-                           int k_layout, int v_layout) {
-    extern __shared__ __align__(16) float xs[];  // Wq + Wk + Wv floats
+                           int k_layout, int v_layout, const float* __restrict__ cs, int rot, int v_unit, float eps_v) {
+    extern __shared__ __align__(16) float xs[];  // Wq + Wk + Wv floats, then G floats when v_unit
     __shared__ float red[32];
     pdl_trigger();
     pdl_wait();
@@ -564,6 +568,71 @@ qkv_bias_norm_store_kernel(const float* __restrict__ qkv, int S, size_t split_st
     const int pos = cache_pos[n];
     const int page = table[(size_t)tok_seq[n] * table_stride + pos / LUMEN_PAGE];
     const int r = pos % LUMEN_PAGE;
+    float* vr = xs + W;
+    if (rot > 0 || v_unit) {
+        // the normed queries and keys go back to shared memory, where the rotation finds a value's
+        // partner; a warp a value head sums that head's squares
+        for (int i = threadIdx.x * V; i < Wq + Wk; i += blockDim.x * V) {
+            Vals<V> x = ldv<V>(xs + i);
+            const float* gw = i < Wq ? qw : kw;
+            if (gw) {
+                const Vals<V> g = ldv<V>(gw + (i < Wq ? i : i - Wq));
+                const float rr = i < Wq ? rq : rk;
+#pragma unroll
+                for (int k = 0; k < V; ++k) x.v[k] = x.v[k] * rr * g.v[k];
+            }
+            stv<V>(xs + i, x);
+        }
+        if (v_unit) {
+            const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarp = blockDim.x >> 5;
+            for (int g = warp; g < G; g += nwarp) {
+                float ss = 0.0f;
+                for (int e = lane; e < dv; e += 32) { const float x = xs[Wq + Wk + g * dv + e]; ss += x * x; }
+                ss = warp_sum(ss);
+                if (lane == 0) vr[g] = 1.0f / sqrtf(ss / (float)dv + eps_v);
+            }
+        }
+        __syncthreads();
+        const int half = rot >> 1;
+        const float* csn = cs + (size_t)n * rot;         // rot/2 pairs of (cos, sin)
+        for (int i = threadIdx.x * V; i < W; i += blockDim.x * V) {
+            Vals<V> x = ldv<V>(xs + i);
+            if (i < Wq + Wk) {
+                const int e0 = (i < Wq ? i : i - Wq) % d;  // place in the head (a group of V stays inside one head)
+                if (e0 < rot) {
+#pragma unroll
+                    for (int k = 0; k < V; ++k) {
+                        const int e = e0 + k;
+                        if (e < half) {
+                            const float c = csn[2 * e], sn = csn[2 * e + 1];
+                            x.v[k] = x.v[k] * c - xs[i + k + half] * sn;
+                        } else if (e < rot) {
+                            const float c = csn[2 * (e - half)], sn = csn[2 * (e - half) + 1];
+                            x.v[k] = x.v[k] * c + xs[i + k - half] * sn;
+                        }
+                    }
+                }
+                if (i < Wq) {
+                    stv<V>(q_out + (size_t)n * Wq + i, x);
+                } else {
+                    const int e = i - Wq, g = e / d, ee = e - g * d;
+                    T* tile = kc + ((size_t)page * G + g) * LUMEN_PAGE * d;
+                    if (V == 1) tile[tile_offset(k_layout, r, ee, d)] = from_f32<T>(x.v[0]);
+                    else stv<V>(tile + (size_t)r * d + ee, x);
+                }
+            } else {
+                const int e = i - Wq - Wk, g = e / dv, ee = e - g * dv;
+                if (v_unit) {
+#pragma unroll
+                    for (int k = 0; k < V; ++k) x.v[k] *= vr[g];
+                }
+                T* tile = vc + ((size_t)page * G + g) * LUMEN_PAGE * dv;
+                if (V == 1) tile[tile_offset(v_layout, r, ee, dv)] = from_f32<T>(x.v[0]);
+                else stv<V>(tile + (size_t)r * dv + ee, x);
+            }
+        }
+        return;
+    }
     for (int i = threadIdx.x * V; i < W; i += blockDim.x * V) {
         Vals<V> x = ldv<V>(xs + i);
         if (i < Wq) {
@@ -596,31 +665,36 @@ template <typename T>
 static void qkv_store_launch(bool v4, int N, int threads, size_t smem, cudaStream_t stream, const float* qkv, int S,
                              size_t stride, const float* bias, const float* qw, const float* kw, float eps,
                              const int* cache_pos, const int* tok_seq, const int* table, int table_stride, T* q_out,
-                             T* kc, T* vc, int Wq, int Wk, int Wv, int G, int d, int dv, int k_layout, int v_layout) {
+                             T* kc, T* vc, int Wq, int Wk, int Wv, int G, int d, int dv, int k_layout, int v_layout,
+                             const float* cs, int rot, int v_unit, float eps_v) {
     if (v4) {
         auto k = qkv_bias_norm_store_kernel<T, 4>;
         if (smem > 40 * 1024) cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         lumen_launch(k, dim3(N), dim3(threads), smem, stream, qkv, S, stride, bias, qw, kw, eps, cache_pos, tok_seq, table,
-                     table_stride, q_out, kc, vc, Wq, Wk, Wv, G, d, dv, k_layout, v_layout);
+                     table_stride, q_out, kc, vc, Wq, Wk, Wv, G, d, dv, k_layout, v_layout, cs, rot, v_unit, eps_v);
     } else {
         auto k = qkv_bias_norm_store_kernel<T, 1>;
         if (smem > 40 * 1024) cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         lumen_launch(k, dim3(N), dim3(threads), smem, stream, qkv, S, stride, bias, qw, kw, eps, cache_pos, tok_seq, table,
-                     table_stride, q_out, kc, vc, Wq, Wk, Wv, G, d, dv, k_layout, v_layout);
+                     table_stride, q_out, kc, vc, Wq, Wk, Wv, G, d, dv, k_layout, v_layout, cs, rot, v_unit, eps_v);
     }
 }
 
+// cs, rot: the rotation's (cos, sin) table [N, rot/2, 2] and the number of rotated values a head
+// (0: no rotation); v_unit: every value head divided by its root mean square (eps_v).
 LUMEN_API int lumen_qkv_bias_norm_store(const float* qkv, int n_split, long long split_stride, const float* bias,
                                         const float* qw, const float* kw, float eps, const int* cache_pos,
                                         const int* tok_seq, const int* table, int table_stride, void* q_out,
                                         void* kc, void* vc, int is_bf16, int N, int Wq, int G, int d, int dv,
-                                        int k_layout, int v_layout, cudaStream_t stream) {
+                                        int k_layout, int v_layout, const float* cs, int rot, int v_unit, float eps_v,
+                                        cudaStream_t stream) {
     if (N <= 0) return 0;
     if (Wq <= 0 || G <= 0 || d <= 0 || dv <= 0 || n_split < 1) return LUMEN_ERR_BAD_ARGUMENT;
+    if (rot < 0 || (rot & 1) || rot > d || (rot > 0 && !cs) || Wq % d) return LUMEN_ERR_BAD_ARGUMENT;
     if ((k_layout == LUMEN_LAYOUT_SW128 && (!is_bf16 || d % 64)) || (v_layout == LUMEN_LAYOUT_SW128 && (!is_bf16 || dv % 64)))
         return LUMEN_ERR_UNSUPPORTED;
     const int Wk = G * d, Wv = G * dv, W = Wq + Wk + Wv;
-    const size_t smem = (size_t)W * sizeof(float);
+    const size_t smem = (size_t)(W + (v_unit ? G : 0)) * sizeof(float);
     if (smem > 200 * 1024) return LUMEN_ERR_UNSUPPORTED;
     const bool v4 = (Wq & 3) == 0 && (d & 3) == 0 && (dv & 3) == 0 && k_layout == LUMEN_LAYOUT_LINEAR &&
                     v_layout == LUMEN_LAYOUT_LINEAR;
@@ -628,11 +702,12 @@ LUMEN_API int lumen_qkv_bias_norm_store(const float* qkv, int n_split, long long
     if (is_bf16)
         qkv_store_launch<__nv_bfloat16>(v4, N, threads, smem, stream, qkv, n_split, (size_t)split_stride, bias, qw, kw,
                                         eps, cache_pos, tok_seq, table, table_stride, (__nv_bfloat16*)q_out,
-                                        (__nv_bfloat16*)kc, (__nv_bfloat16*)vc, Wq, Wk, Wv, G, d, dv, k_layout, v_layout);
+                                        (__nv_bfloat16*)kc, (__nv_bfloat16*)vc, Wq, Wk, Wv, G, d, dv, k_layout, v_layout,
+                                        cs, rot, v_unit, eps_v);
     else
         qkv_store_launch<float>(v4, N, threads, smem, stream, qkv, n_split, (size_t)split_stride, bias, qw, kw, eps,
                                 cache_pos, tok_seq, table, table_stride, (float*)q_out, (float*)kc, (float*)vc, Wq, Wk,
-                                Wv, G, d, dv, k_layout, v_layout);
+                                Wv, G, d, dv, k_layout, v_layout, cs, rot, v_unit, eps_v);
     LUMEN_LAUNCH_CHECK();
     return 0;
 }

@@ -1,0 +1,275 @@
+// A feed-forward made of many small experts of which each token uses a few.
+//   1. route: softmax over the router's logits (float32), choice by score + a correction, the
+//      chosen experts' scores (without the correction) times a scale as weights.
+//   2. group: the step's (token, choice) entries put in order of their expert, and the list of
+//      row tiles (expert, first entry, number of entries) that the products walk. Everything
+//      stays on the device: the products are launched with as many blocks as any routing can
+//      need, and the blocks beyond the list leave.
+//   3. two grouped products: gate and up with SiLU(gate) * up behind them, then down with the
+//      entry's weight, written to out[choice][token][:] so that the consumer adds a token's
+//      choices in rising order, like the partial sums of a split product.
+//   4. identity experts (indices from n_experts on): out[choice][token][:] = weight * input.
+// Every output element is one dot product summed over k in rising order by one thread, so it
+// depends on its own row and the expert's weights only, never on the batch or on the order in
+// which the entries of an expert were listed.
+#include "common.cuh"
+
+#define MOE_MAX_LANE_VALS 16      // router outputs a lane holds: up to 512 experts
+#define MOE_MAX_EXPERTS 1024
+#define MOE_TM 32                 // entries a row tile
+#define MOE_TN 64                 // output columns a block
+#define MOE_TK 32
+
+// ---------------------------------------------------------------- route
+// A warp a token. logits float32 [N, Et]; corr float32 [Et] or null; idx int32 [N, top];
+// wt float32 [N, top]. Equal choice scores go to the lower index.
+__global__ void __launch_bounds__(128)
+moe_route_kernel(const float* __restrict__ logits, const float* __restrict__ corr, int Et, int top, float scale,
+                 int* __restrict__ idx, float* __restrict__ wt, int N) {
+    pdl_trigger();
+    pdl_wait();
+    const int lane = threadIdx.x & 31;
+    const int t = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    if (t >= N) return;
+    float s[MOE_MAX_LANE_VALS], c[MOE_MAX_LANE_VALS];
+    float m = -INFINITY;
+#pragma unroll
+    for (int r = 0; r < MOE_MAX_LANE_VALS; ++r) {
+        const int e = lane + 32 * r;
+        s[r] = e < Et ? logits[(size_t)t * Et + e] : -INFINITY;
+        m = fmaxf(m, s[r]);
+    }
+    m = warp_max(m);
+    float sum = 0.0f;
+#pragma unroll
+    for (int r = 0; r < MOE_MAX_LANE_VALS; ++r) {
+        const int e = lane + 32 * r;
+        s[r] = e < Et ? expf(s[r] - m) : 0.0f;
+        sum += s[r];
+    }
+    sum = warp_sum(sum);
+    const float inv = 1.0f / sum;
+#pragma unroll
+    for (int r = 0; r < MOE_MAX_LANE_VALS; ++r) {
+        const int e = lane + 32 * r;
+        s[r] *= inv;
+        c[r] = e < Et ? s[r] + (corr ? corr[e] : 0.0f) : -INFINITY;
+    }
+    for (int k = 0; k < top; ++k) {
+        float best = -INFINITY, best_s = 0.0f;
+        int best_e = 0x7fffffff;
+#pragma unroll
+        for (int r = 0; r < MOE_MAX_LANE_VALS; ++r) {
+            const int e = lane + 32 * r;
+            if (e < Et && (c[r] > best || (c[r] == best && e < best_e))) { best = c[r]; best_e = e; best_s = s[r]; }
+        }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+            const float ob = __shfl_xor_sync(0xffffffffu, best, o);
+            const int oe = __shfl_xor_sync(0xffffffffu, best_e, o);
+            const float os = __shfl_xor_sync(0xffffffffu, best_s, o);
+            if (ob > best || (ob == best && oe < best_e)) { best = ob; best_e = oe; best_s = os; }
+        }
+#pragma unroll
+        for (int r = 0; r < MOE_MAX_LANE_VALS; ++r)
+            if (lane + 32 * r == best_e) c[r] = -INFINITY;        // taken
+        if (lane == 0) {
+            idx[(size_t)t * top + k] = best_e;
+            wt[(size_t)t * top + k] = best_s * scale;
+        }
+    }
+}
+
+LUMEN_API int lumen_moe_route(const float* logits, const float* corr, int Et, int top, float scale, int* idx,
+                              float* wt, int N, cudaStream_t stream) {
+    if (N <= 0) return 0;
+    if (Et <= 0 || top <= 0 || top > Et) return LUMEN_ERR_BAD_ARGUMENT;
+    if (Et > 32 * MOE_MAX_LANE_VALS) return LUMEN_ERR_UNSUPPORTED;
+    lumen_launch(moe_route_kernel, dim3((N + 3) / 4), dim3(128), 0, stream, logits, corr, Et, top, scale, idx, wt, N);
+    LUMEN_LAUNCH_CHECK();
+    return 0;
+}
+
+// ---------------------------------------------------------------- group
+// One block. entries = N * top; sorted int32 [entries] receives the entries (token * top +
+// choice) of expert 0, then of expert 1, ...; entries of identity experts (idx >= E) are left
+// out. tiles int32 [max_tiles, 3] = (expert, first place in sorted, count <= MOE_TM);
+// n_tiles int32 [1].
+__global__ void __launch_bounds__(1024)
+moe_group_kernel(const int* __restrict__ idx, int entries, int E, int* __restrict__ sorted, int* __restrict__ tiles,
+                 int* __restrict__ n_tiles) {
+    __shared__ int count[MOE_MAX_EXPERTS], start[MOE_MAX_EXPERTS];
+    pdl_trigger();
+    pdl_wait();
+    for (int e = threadIdx.x; e < E; e += blockDim.x) count[e] = 0;
+    __syncthreads();
+    for (int i = threadIdx.x; i < entries; i += blockDim.x) {
+        const int e = idx[i];
+        if (e >= 0 && e < E) atomicAdd(&count[e], 1);
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        int at = 0, nt = 0;
+        for (int e = 0; e < E; ++e) {
+            const int c = count[e];
+            start[e] = at;
+            for (int o = 0; o < c; o += MOE_TM) {
+                tiles[3 * nt] = e;
+                tiles[3 * nt + 1] = at + o;
+                tiles[3 * nt + 2] = min(MOE_TM, c - o);
+                ++nt;
+            }
+            at += c;
+            count[e] = 0;             // from here on: entries of e placed so far
+        }
+        *n_tiles = nt;
+    }
+    __syncthreads();
+    for (int i = threadIdx.x; i < entries; i += blockDim.x) {
+        const int e = idx[i];
+        if (e >= 0 && e < E) sorted[start[e] + atomicAdd(&count[e], 1)] = i;
+    }
+}
+
+LUMEN_API int lumen_moe_tile_rows() { return MOE_TM; }
+
+LUMEN_API int lumen_moe_group(const int* idx, int entries, int E, int* sorted, int* tiles, int* n_tiles,
+                              cudaStream_t stream) {
+    if (entries <= 0) return 0;
+    if (E <= 0 || E > MOE_MAX_EXPERTS) return LUMEN_ERR_UNSUPPORTED;
+    lumen_launch(moe_group_kernel, dim3(1), dim3(1024), 0, stream, idx, entries, E, sorted, tiles, n_tiles);
+    LUMEN_LAUNCH_CHECK();
+    return 0;
+}
+
+// ---------------------------------------------------------------- grouped products
+// Block (tile, column block): the tile's entries x MOE_TN output columns of the tile's expert.
+// GATED: the rows of the activations are tokens (entry / top); W is [E, 2 F, K], gate rows
+//   first; out[entry, f] = silu(gate) * up, in the activations' type.
+// else:  the rows of the activations are entries; W is [E, Nout, K]; out is float32
+//   [top, tokens, Nout] and receives weight[entry] * product at [entry % top][entry / top].
+// 256 threads; a thread holds 2 rows x 4 columns (of gate and of up when GATED).
+template <typename TA, typename TW, bool GATED>
+__global__ void __launch_bounds__(256)
+moe_product_kernel(const TA* __restrict__ A, const TW* __restrict__ W, const int* __restrict__ sorted,
+                   const int* __restrict__ tiles, const int* __restrict__ n_tiles, const float* __restrict__ wt,
+                   void* __restrict__ out, int K, int Nout, int top, int n_tokens) {
+    __shared__ float As[MOE_TK][MOE_TM + 1];
+    __shared__ float Ws[GATED ? 2 : 1][MOE_TK][MOE_TN + 1];
+    __shared__ int rows[MOE_TM];
+    pdl_trigger();
+    pdl_wait();
+    const int tile = blockIdx.x;
+    if (tile >= *n_tiles) return;
+    const int e = tiles[3 * tile], first = tiles[3 * tile + 1], cnt = tiles[3 * tile + 2];
+    const int n0 = blockIdx.y * MOE_TN;
+    const int tid = threadIdx.x, tx = tid & 15, ty = tid >> 4;
+    if (tid < MOE_TM) rows[tid] = tid < cnt ? sorted[first + tid] : -1;
+    __syncthreads();
+    const TW* We = W + (size_t)e * (GATED ? 2 : 1) * Nout * K;
+    float acc[GATED ? 2 : 1][2][4];
+#pragma unroll
+    for (int m = 0; m < (GATED ? 2 : 1); ++m)
+#pragma unroll
+        for (int i = 0; i < 2; ++i)
+#pragma unroll
+            for (int jn = 0; jn < 4; ++jn) acc[m][i][jn] = 0.0f;
+    for (int k0 = 0; k0 < K; k0 += MOE_TK) {
+        // activations: 32 rows x 32 k, 4 a thread; weights: 64 rows x 32 k (x 2), 8 (16) a thread
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const int li = tid + i * 256, r = li >> 5, kk = li & 31;
+            const int entry = rows[r];
+            float v = 0.0f;
+            if (entry >= 0 && k0 + kk < K) v = to_f32(A[(size_t)(GATED ? entry / top : entry) * K + k0 + kk]);
+            As[kk][r] = v;
+        }
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+            const int li = tid + i * 256, r = li >> 5, kk = li & 31;
+            const bool ok = n0 + r < Nout && k0 + kk < K;
+            Ws[0][kk][r] = ok ? to_f32(We[(size_t)(n0 + r) * K + k0 + kk]) : 0.0f;
+            if (GATED) Ws[GATED ? 1 : 0][kk][r] = ok ? to_f32(We[(size_t)(Nout + n0 + r) * K + k0 + kk]) : 0.0f;
+        }
+        __syncthreads();
+#pragma unroll
+        for (int kk = 0; kk < MOE_TK; ++kk) {
+            const float a0 = As[kk][ty * 2], a1 = As[kk][ty * 2 + 1];
+#pragma unroll
+            for (int m = 0; m < (GATED ? 2 : 1); ++m)
+#pragma unroll
+                for (int jn = 0; jn < 4; ++jn) {
+                    const float w = Ws[m][kk][tx * 4 + jn];
+                    acc[m][0][jn] = fmaf(a0, w, acc[m][0][jn]);
+                    acc[m][1][jn] = fmaf(a1, w, acc[m][1][jn]);
+                }
+        }
+        __syncthreads();
+    }
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+        const int entry = rows[ty * 2 + i];
+        if (entry < 0) continue;
+#pragma unroll
+        for (int jn = 0; jn < 4; ++jn) {
+            const int n = n0 + tx * 4 + jn;
+            if (n >= Nout) continue;
+            if (GATED) {
+                const float g = acc[0][i][jn], u = acc[GATED ? 1 : 0][i][jn];
+                ((TA*)out)[(size_t)entry * Nout + n] = from_f32<TA>(g / (1.0f + expf(-g)) * u);
+            } else {
+                ((float*)out)[((size_t)(entry % top) * n_tokens + entry / top) * Nout + n] = wt[entry] * acc[0][i][jn];
+            }
+        }
+    }
+}
+
+// gated != 0: A [tokens, K] -> out [entries, Nout] of A's type, W [E, 2 Nout, K];
+// gated == 0: A [entries, K] -> out float32 [top, tokens, Nout], W [E, Nout, K].
+LUMEN_API int lumen_moe_product(const void* A, int a_is_bf16, const void* W, int w_is_bf16, const int* sorted,
+                                const int* tiles, const int* n_tiles, int max_tiles, const float* wt, void* out,
+                                int K, int Nout, int top, int n_tokens, int gated, cudaStream_t stream) {
+    if (max_tiles <= 0 || n_tokens <= 0) return 0;
+    if (K <= 0 || Nout <= 0 || top <= 0) return LUMEN_ERR_BAD_ARGUMENT;
+    dim3 grid(max_tiles, (Nout + MOE_TN - 1) / MOE_TN);
+    if (grid.y > 65535) return LUMEN_ERR_UNSUPPORTED;
+#define MOE_GO(TA, TW, GATED)                                                                                        \
+    lumen_launch(moe_product_kernel<TA, TW, GATED>, grid, dim3(256), 0, stream, (const TA*)A, (const TW*)W, sorted, \
+                 tiles, n_tiles, wt, out, K, Nout, top, n_tokens)
+    if (a_is_bf16 && w_is_bf16) { if (gated) MOE_GO(__nv_bfloat16, __nv_bfloat16, true); else MOE_GO(__nv_bfloat16, __nv_bfloat16, false); }
+    else if (!a_is_bf16 && w_is_bf16) { if (gated) MOE_GO(float, __nv_bfloat16, true); else MOE_GO(float, __nv_bfloat16, false); }
+    else if (!a_is_bf16 && !w_is_bf16) { if (gated) MOE_GO(float, float, true); else MOE_GO(float, float, false); }
+    else return LUMEN_ERR_UNSUPPORTED;
+#undef MOE_GO
+    LUMEN_LAUNCH_CHECK();
+    return 0;
+}
+
+// ---------------------------------------------------------------- identity experts
+// out[k][t][:] = wt[t, k] * x[t][:] for the entries whose expert index is >= E.
+template <typename TA>
+__global__ void moe_identity_kernel(const TA* __restrict__ x, const int* __restrict__ idx, const float* __restrict__ wt,
+                                    float* __restrict__ out, int E, int top, int n_tokens, int D) {
+    pdl_trigger();
+    pdl_wait();
+    const int entry = blockIdx.x;
+    if (idx[entry] < E) return;
+    const int t = entry / top, k = entry % top;
+    const float w = wt[entry];
+    float* o = out + ((size_t)k * n_tokens + t) * D;
+    for (int i = threadIdx.x; i < D; i += blockDim.x) o[i] = w * to_f32(x[(size_t)t * D + i]);
+}
+
+LUMEN_API int lumen_moe_identity(const void* x, int x_is_bf16, const int* idx, const float* wt, float* out, int E,
+                                 int top, int n_tokens, int D, cudaStream_t stream) {
+    if (n_tokens <= 0) return 0;
+    if (D <= 0 || top <= 0) return LUMEN_ERR_BAD_ARGUMENT;
+    if (x_is_bf16)
+        lumen_launch(moe_identity_kernel<__nv_bfloat16>, dim3(n_tokens * top), dim3(128), 0, stream,
+                     (const __nv_bfloat16*)x, idx, wt, out, E, top, n_tokens, D);
+    else
+        lumen_launch(moe_identity_kernel<float>, dim3(n_tokens * top), dim3(128), 0, stream, (const float*)x, idx, wt, out,
+                     E, top, n_tokens, D);
+    LUMEN_LAUNCH_CHECK();
+    return 0;
+}

@@ -1,0 +1,340 @@
+// Kernels of a selective state-space mixer (a linear recurrence over time with a matrix state
+// per head) and of the element-wise pieces around it:
+//   - the short causal convolution, with bias and SiLU, of some columns of the input
+//     projection, whose last inputs are part of a sequence's state,
+//   - the recurrence S_t = a_t S_(t-1) + dt_t B_t x_t^T, y_t = S_t^T C_t + D x_t,
+//   - the gate y * silu(z) followed by an RMS norm in equal parts of the row,
+//   - xIELU, an activation with two learned numbers.
+// All arithmetic is float32 with the precise exponentials. The input projection arrives as the
+// S partial sums of a split matrix product, [S, rows, width], which are added in rising order
+// of S wherever a value is read. A step brings cu_q[b+1] - cu_q[b] tokens of sequence b (any
+// number, also none); state lives in row seq_slot[b] of its store.
+#include "common.cuh"
+
+#define SSM_MAX_TAPS 16
+
+__device__ __forceinline__ float sum_parts(const float* p, int S, size_t stride) {
+    float x = p[0];
+    for (int s = 1; s < S; ++s) x += p[(size_t)s * stride];
+    return x;
+}
+__device__ __forceinline__ float silu_f(float x) { return x / (1.0f + expf(-x)); }
+__device__ __forceinline__ float softplus_f(float x) { return x > 20.0f ? x : log1pf(expf(x)); }
+
+// ---------------------------------------------------------------- convolution + bias + SiLU
+// out[t, c] = silu(bias[c] + sum_j w[j, c] * in[t - taps + 1 + j, c]) for the C columns of the
+// projection that start at column c0; in[] before the step's first token of the sequence comes
+// from state[slot][taps - 1 + (t' - first)] (rows oldest to newest, zeros for a new sequence).
+// The state is not written here (conv_state_kernel does, after every reader is done).
+__global__ void __launch_bounds__(256)
+conv_silu_kernel(const float* __restrict__ u, int S, size_t split_stride, int Wu, int c0, int C,
+                 const float* __restrict__ w, const float* __restrict__ bias, int taps,
+                 const float* __restrict__ state, size_t slot_stride, const int* __restrict__ tok_seq,
+                 const int* __restrict__ cu_q, const int* __restrict__ seq_slot, float* __restrict__ out, int N) {
+    pdl_trigger();
+    pdl_wait();
+    const int c = blockIdx.x * blockDim.x + threadIdx.x;
+    const int t = blockIdx.y;
+    if (c >= C || t >= N) return;
+    const int b = tok_seq[t];
+    const int first = cu_q[b];
+    const float* st = state + (size_t)seq_slot[b] * slot_stride;
+    float acc = bias ? bias[c] : 0.0f;
+    for (int j = 0; j < taps; ++j) {
+        const int src = t - taps + 1 + j;
+        float x;
+        if (src >= first) x = sum_parts(u + (size_t)src * Wu + c0 + c, S, split_stride);
+        else x = st[(size_t)(taps - 1 + src - first) * C + c];
+        acc = fmaf(w[(size_t)j * C + c], x, acc);
+    }
+    out[(size_t)t * C + c] = silu_f(acc);
+}
+
+// The state moved on to the end of the step: its rows become the last taps - 1 inputs of the
+// sequence, taken from the step's rows and, where the step brought fewer, from the old state.
+__global__ void __launch_bounds__(256)
+conv_state_kernel(const float* __restrict__ u, int S, size_t split_stride, int Wu, int c0, int C, int taps,
+                  float* __restrict__ state, size_t slot_stride, const int* __restrict__ cu_q,
+                  const int* __restrict__ seq_slot) {
+    pdl_trigger();
+    pdl_wait();
+    const int c = blockIdx.x * blockDim.x + threadIdx.x;
+    const int b = blockIdx.y;
+    if (c >= C) return;
+    const int first = cu_q[b], qlen = cu_q[b + 1] - first;
+    if (qlen <= 0) return;
+    float* st = state + (size_t)seq_slot[b] * slot_stride;
+    float v[SSM_MAX_TAPS];
+#pragma unroll
+    for (int r = 0; r < SSM_MAX_TAPS - 1; ++r) {
+        if (r < taps - 1) {
+            const int li = qlen - (taps - 1) + r;
+            v[r] = li >= 0 ? sum_parts(u + (size_t)(first + li) * Wu + c0 + c, S, split_stride)
+                           : st[(size_t)(r + qlen) * C + c];
+        }
+    }
+#pragma unroll
+    for (int r = 0; r < SSM_MAX_TAPS - 1; ++r)
+        if (r < taps - 1) st[(size_t)r * C + c] = v[r];
+}
+
+// One token a sequence (row b is sequence b's): convolution and state in one pass, a thread a
+// (sequence, column), which reads the state, uses it and shifts it.
+__global__ void __launch_bounds__(256)
+conv_silu_decode_kernel(const float* __restrict__ u, int S, size_t split_stride, int Wu, int c0, int C,
+                        const float* __restrict__ w, const float* __restrict__ bias, int taps,
+                        float* __restrict__ state, size_t slot_stride, const int* __restrict__ seq_slot,
+                        float* __restrict__ out, int N) {
+    pdl_trigger();
+    pdl_wait();
+    const int c = blockIdx.x * blockDim.x + threadIdx.x;
+    const int t = blockIdx.y;
+    if (c >= C || t >= N) return;
+    float* st = state + (size_t)seq_slot[t] * slot_stride;
+    const float x = sum_parts(u + (size_t)t * Wu + c0 + c, S, split_stride);
+    float acc = bias ? bias[c] : 0.0f;
+    float v[SSM_MAX_TAPS];
+#pragma unroll
+    for (int r = 0; r < SSM_MAX_TAPS - 1; ++r)
+        if (r < taps - 1) {
+            v[r] = st[(size_t)r * C + c];
+            acc = fmaf(w[(size_t)r * C + c], v[r], acc);
+        }
+    acc = fmaf(w[(size_t)(taps - 1) * C + c], x, acc);
+#pragma unroll
+    for (int r = 0; r < SSM_MAX_TAPS - 1; ++r)
+        if (r < taps - 1) st[(size_t)r * C + c] = (r + 1 < taps - 1) ? v[r + 1] : x;
+    out[(size_t)t * C + c] = silu_f(acc);
+}
+
+LUMEN_API int lumen_conv_silu(const float* u, int n_split, long long split_stride, int Wu, int c0, int C,
+                              const float* w, const float* bias, int taps, float* state, long long slot_stride,
+                              const int* tok_seq, const int* cu_q, const int* seq_slot, int n_seqs, int decode,
+                              float* out, int N, cudaStream_t stream) {
+    if (N <= 0) return 0;
+    if (C <= 0 || taps < 1 || taps > SSM_MAX_TAPS || n_split < 1 || c0 < 0 || c0 + C > Wu || (taps > 1 && !state))
+        return LUMEN_ERR_BAD_ARGUMENT;
+    if (N > 65535 || n_seqs > 65535) return LUMEN_ERR_UNSUPPORTED;
+    dim3 grid((C + 255) / 256, N);
+    if (decode) {
+        lumen_launch(conv_silu_decode_kernel, grid, dim3(256), 0, stream, u, n_split, (size_t)split_stride, Wu, c0, C, w,
+                     bias, taps, state, (size_t)slot_stride, seq_slot, out, N);
+        LUMEN_LAUNCH_CHECK();
+        return 0;
+    }
+    lumen_launch(conv_silu_kernel, grid, dim3(256), 0, stream, u, n_split, (size_t)split_stride, Wu, c0, C, w, bias, taps,
+                 (const float*)state, (size_t)slot_stride, tok_seq, cu_q, seq_slot, out, N);
+    LUMEN_LAUNCH_CHECK();
+    if (taps > 1) {
+        lumen_launch(conv_state_kernel, dim3((C + 255) / 256, n_seqs), dim3(256), 0, stream, u, n_split,
+                     (size_t)split_stride, Wu, c0, C, taps, state, (size_t)slot_stride, cu_q, seq_slot);
+        LUMEN_LAUNCH_CHECK();
+    }
+    return 0;
+}
+
+// ---------------------------------------------------------------- the recurrence
+// A block takes one (sequence, head) and PB of the head's P channels, and walks the sequence's
+// tokens of this step in order. Thread (p, j), j < NS, keeps the state values S[n, p] with
+// n = j + NS r, r < R, in registers (NS a power of two up to 32, R up to SSM_R): it decays
+// them, adds dt B[n] x[p], and sums S[n, p] C[n] over its n; the NS threads of a channel add
+// their sums by shuffles in a fixed order. Tokens are staged SSM_CHUNK at a time in shared
+// memory (x, B, C of the head's group, and dt and the decay, which the first threads make from
+// the projection's dt column: dt = softplus(sum + dt_bias), a = exp(-exp(A_log) dt)). The order
+// of every sum depends on the sizes alone, so a token's result is the same however the
+// sequence was cut into steps and whatever else is in the batch.
+#define SSM_R 32
+#define SSM_CHUNK 16
+
+__global__ void __launch_bounds__(1024)
+ssm_scan_kernel(const float* __restrict__ xbc, int C, int inner, int H, int P, int Nst, int G,
+                const float* __restrict__ u, int S, size_t split_stride, int Wu, int cdt,
+                const float* __restrict__ dt_bias, const float* __restrict__ A_log, const float* __restrict__ Dskip,
+                float* __restrict__ state, size_t slot_stride, const int* __restrict__ cu_q,
+                const int* __restrict__ seq_slot, float* __restrict__ y, int PB, int NS) {
+    extern __shared__ __align__(16) float sm[];
+    pdl_trigger();
+    pdl_wait();
+    const int b = blockIdx.x, h = blockIdx.y, p0 = blockIdx.z * PB;
+    const int first = cu_q[b], qlen = cu_q[b + 1] - first;
+    if (qlen <= 0) return;
+    const int tid = threadIdx.x, j = tid % NS, pl = tid / NS, p = p0 + pl;
+    const bool live = pl < PB && p < P;
+    const int g = h / (H / G);
+    const int R = (Nst + NS - 1) / NS;
+    float* xs = sm;                                  // [CHUNK][PB]
+    float* Bs = xs + SSM_CHUNK * PB;                 // [CHUNK][Nst]
+    float* Cs = Bs + SSM_CHUNK * Nst;                // [CHUNK][Nst]
+    float* dts = Cs + SSM_CHUNK * Nst;               // [CHUNK]
+    float* decs = dts + SSM_CHUNK;                   // [CHUNK]
+    float* st = state + (size_t)seq_slot[b] * slot_stride + (size_t)h * Nst * P;
+    float s[SSM_R];
+#pragma unroll
+    for (int r = 0; r < SSM_R; ++r) {
+        const int n = j + NS * r;
+        s[r] = (live && r < R && n < Nst) ? st[(size_t)n * P + p] : 0.0f;
+    }
+    const float a_h = -expf(A_log[h]), bias_h = dt_bias[h], d_h = Dskip[h];
+    for (int t0 = 0; t0 < qlen; t0 += SSM_CHUNK) {
+        const int nt = min(SSM_CHUNK, qlen - t0);
+        __syncthreads();
+        for (int i = tid; i < nt * PB; i += blockDim.x) {
+            const int tt = i / PB, pp = i - tt * PB;
+            xs[i] = (p0 + pp < P) ? xbc[(size_t)(first + t0 + tt) * C + h * P + p0 + pp] : 0.0f;
+        }
+        for (int i = tid; i < nt * Nst; i += blockDim.x) {
+            const int tt = i / Nst, n = i - tt * Nst;
+            const float* row = xbc + (size_t)(first + t0 + tt) * C + inner + g * Nst + n;
+            Bs[i] = row[0];
+            Cs[i] = row[(size_t)G * Nst];
+        }
+        if (tid < nt) {
+            const float dt = softplus_f(sum_parts(u + (size_t)(first + t0 + tid) * Wu + cdt + h, S, split_stride) + bias_h);
+            dts[tid] = dt;
+            decs[tid] = expf(a_h * dt);
+        }
+        __syncthreads();
+        for (int tt = 0; tt < nt; ++tt) {
+            const float dec = decs[tt], x = live ? xs[tt * PB + pl] : 0.0f, dx = dts[tt] * x;
+            const float* Bt = Bs + tt * Nst;
+            const float* Ct = Cs + tt * Nst;
+            float acc = 0.0f;
+#pragma unroll
+            for (int r = 0; r < SSM_R; ++r) {
+                const int n = j + NS * r;
+                if (r < R && n < Nst) {
+                    s[r] = fmaf(dec, s[r], dx * Bt[n]);
+                    acc = fmaf(s[r], Ct[n], acc);
+                }
+            }
+            for (int o = NS >> 1; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
+            if (live && j == 0) y[(size_t)(first + t0 + tt) * inner + h * P + p] = fmaf(d_h, x, acc);
+        }
+    }
+#pragma unroll
+    for (int r = 0; r < SSM_R; ++r) {
+        const int n = j + NS * r;
+        if (live && r < R && n < Nst) st[(size_t)n * P + p] = s[r];
+    }
+}
+
+// xbc float32 [N, C] with C = inner + 2 G Nst (x, then B, then C of every group); u the input
+// projection's partial sums [S, N, Wu], whose columns cdt .. cdt + H - 1 are dt; state float32
+// [slots, H, Nst, P]; y float32 [N, inner].
+LUMEN_API int lumen_ssm_scan(const float* xbc, int H, int P, int Nst, int G, const float* u, int n_split,
+                             long long split_stride, int Wu, int cdt, const float* dt_bias, const float* A_log,
+                             const float* Dskip, float* state, long long slot_stride, const int* cu_q,
+                             const int* seq_slot, int n_seqs, float* y, int N, cudaStream_t stream) {
+    if (N <= 0 || n_seqs <= 0) return 0;
+    if (H <= 0 || P <= 0 || Nst <= 0 || G <= 0 || H % G || n_split < 1 || cdt < 0 || cdt + H > Wu)
+        return LUMEN_ERR_BAD_ARGUMENT;
+    if (Nst > 32 * SSM_R || H > 65535) return LUMEN_ERR_UNSUPPORTED;
+    int NS = 1;
+    while (NS * SSM_R < Nst) NS <<= 1;
+    int PB = P < 1024 / NS ? P : 1024 / NS;
+    // more blocks than SMs where a step has few (sequence, head) pairs: a head's channels are
+    // independent of one another, so how they are dealt out changes no result
+    while ((long long)n_seqs * H * ((P + PB - 1) / PB) < 2 * 148 && PB * NS > 64 && PB % 2 == 0) PB /= 2;
+    const int zb = (P + PB - 1) / PB;
+    if (zb > 65535) return LUMEN_ERR_UNSUPPORTED;
+    int threads = ((PB * NS + 31) / 32) * 32;
+    const int inner = H * P, C = inner + 2 * G * Nst;
+    const size_t smem = (size_t)(SSM_CHUNK * (PB + 2 * Nst) + 2 * SSM_CHUNK) * sizeof(float);
+    if (smem > 200 * 1024) return LUMEN_ERR_UNSUPPORTED;
+    if (smem > 48 * 1024) cudaFuncSetAttribute(ssm_scan_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    lumen_launch(ssm_scan_kernel, dim3(n_seqs, H, zb), dim3(threads), smem, stream, xbc, C, inner, H, P, Nst, G, u, n_split,
+                 (size_t)split_stride, Wu, cdt, dt_bias, A_log, Dskip, state, (size_t)slot_stride, cu_q, seq_slot, y, PB,
+                 NS);
+    LUMEN_LAUNCH_CHECK();
+    return 0;
+}
+
+// ---------------------------------------------------------------- gate, then RMS norm in parts
+// v = y * silu(z), z = columns c0 .. c0 + W - 1 of the projection's partial sums; the row is cut
+// into `parts` equal pieces, each divided by its own root mean square (eps inside the root) and
+// multiplied by w. A warp takes a piece at a time.
+template <typename TOut>
+__global__ void __launch_bounds__(1024)
+gated_part_norm_kernel(const float* __restrict__ y, const float* __restrict__ u, int S, size_t split_stride, int Wu,
+                       int c0, const float* __restrict__ w, float eps, int W, int parts, TOut* __restrict__ out) {
+    extern __shared__ __align__(16) float vs[];      // W floats
+    pdl_trigger();
+    pdl_wait();
+    const int t = blockIdx.x;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarp = blockDim.x >> 5;
+    const int len = W / parts;
+    for (int g = warp; g < parts; g += nwarp) {
+        float ss = 0.0f;
+        for (int e = lane; e < len; e += 32) {
+            const int i = g * len + e;
+            const float z = sum_parts(u + (size_t)t * Wu + c0 + i, S, split_stride);
+            const float v = y[(size_t)t * W + i] * silu_f(z);
+            vs[i] = v;
+            ss += v * v;
+        }
+        ss = warp_sum(ss);
+        const float r = 1.0f / sqrtf(ss / (float)len + eps);
+        for (int e = lane; e < len; e += 32) {
+            const int i = g * len + e;
+            out[(size_t)t * W + i] = from_f32<TOut>(vs[i] * r * w[i]);
+        }
+    }
+}
+
+LUMEN_API int lumen_gated_part_norm(const float* y, const float* u, int n_split, long long split_stride, int Wu,
+                                    int c0, const float* w, float eps, int W, int parts, void* out, int out_is_bf16,
+                                    int N, cudaStream_t stream) {
+    if (N <= 0) return 0;
+    if (W <= 0 || parts <= 0 || W % parts || n_split < 1 || c0 < 0 || c0 + W > Wu) return LUMEN_ERR_BAD_ARGUMENT;
+    const size_t smem = (size_t)W * sizeof(float);
+    if (smem > 200 * 1024) return LUMEN_ERR_UNSUPPORTED;
+    int threads = parts * 32;
+    if (threads > 1024) threads = 1024;
+    if (threads < 32) threads = 32;
+    if (out_is_bf16) {
+        auto k = gated_part_norm_kernel<__nv_bfloat16>;
+        if (smem > 48 * 1024) cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        lumen_launch(k, dim3(N), dim3(threads), smem, stream, y, u, n_split, (size_t)split_stride, Wu, c0, w, eps, W,
+                     parts, (__nv_bfloat16*)out);
+    } else {
+        auto k = gated_part_norm_kernel<float>;
+        if (smem > 48 * 1024) cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        lumen_launch(k, dim3(N), dim3(threads), smem, stream, y, u, n_split, (size_t)split_stride, Wu, c0, w, eps, W,
+                     parts, (float*)out);
+    }
+    LUMEN_LAUNCH_CHECK();
+    return 0;
+}
+
+// ---------------------------------------------------------------- xIELU
+// z > 0: softplus(p) z^2 + z / 2;  z <= 0: (1/2 + softplus(q)) (e^z - 1 - z) + z / 2, with
+// (p, q) = act[0], act[1]. z arrives as partial sums [S, total].
+template <typename TOut>
+__global__ void xielu_kernel(const float* __restrict__ z, int S, size_t split_stride, const float* __restrict__ act,
+                             TOut* __restrict__ out, long long total) {
+    pdl_trigger();
+    pdl_wait();
+    const float ap = softplus_f(act[0]), aq = 0.5f + softplus_f(act[1]);
+    const long long step = (long long)gridDim.x * blockDim.x;
+    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += step) {
+        const float x = sum_parts(z + i, S, split_stride);
+        const float r = x > 0.0f ? fmaf(ap * x, x, 0.5f * x) : fmaf(aq, expm1f(x) - x, 0.5f * x);
+        out[i] = from_f32<TOut>(r);
+    }
+}
+
+LUMEN_API int lumen_xielu(const float* z, int n_split, long long split_stride, const float* act, void* out,
+                          int out_is_bf16, long long total, cudaStream_t stream) {
+    if (total <= 0) return 0;
+    if (n_split < 1 || !act) return LUMEN_ERR_BAD_ARGUMENT;
+    long long blocks = (total + 255) / 256;
+    if (blocks > 148 * 16) blocks = 148 * 16;
+    if (out_is_bf16)
+        lumen_launch(xielu_kernel<__nv_bfloat16>, dim3((int)blocks), dim3(256), 0, stream, z, n_split, (size_t)split_stride,
+                     act, (__nv_bfloat16*)out, total);
+    else
+        lumen_launch(xielu_kernel<float>, dim3((int)blocks), dim3(256), 0, stream, z, n_split, (size_t)split_stride, act,
+                     (float*)out, total);
+    LUMEN_LAUNCH_CHECK();
+    return 0;
+}

@@ -181,10 +181,14 @@ def polynorm(z, act, eps, out_dtype):
 
 
 def qkv_bias_norm_store(qkv, bias, q_norm_w, k_norm_w, eps, cache_pos, tok_seq, block_table, kcache, vcache,
-                        nq, nkv, d, dv, out_dtype, k_layout=LAYOUT_LINEAR, v_layout=LAYOUT_LINEAR):
+                        nq, nkv, d, dv, out_dtype, k_layout=LAYOUT_LINEAR, v_layout=LAYOUT_LINEAR,
+                        cs=None, rotary_dim=0, value_unit_eps=None):
     """Bias, one RMS norm over the WHOLE query projection (weight [nq * d]) and one over the whole
     key projection (weight [nkv * d]), q out as [N, nq, d], k and v written to the paged cache
-    (keys [pages, nkv, PAGE, d], values [pages, nkv, PAGE, dv]).
+    (keys [pages, nkv, PAGE, d], values [pages, nkv, PAGE, dv]). With rotary_dim > 0 the first
+    rotary_dim values of every query and key head are rotated after the norm by the angles of
+    `cs` (rope_table: float32 [N, rotary_dim/2, 2]); with value_unit_eps every value head is
+    divided by its root mean square (that eps inside the root).
     qkv float32 [N, nq*d + nkv*d + nkv*dv] or [S, N, ...] partials; bias float32 of that width or None."""
     qkv, S = _partials(qkv, "qkv_bias_norm_store.qkv")
     N = qkv.shape[1]
@@ -206,13 +210,19 @@ def qkv_bias_norm_store(qkv, bias, q_norm_w, k_norm_w, eps, cache_pos, tok_seq, 
     if tuple(kcache.shape[1:]) != (nkv, PAGE, d) or tuple(vcache.shape[1:]) != (nkv, PAGE, dv):
         raise KernelError(f"qkv_bias_norm_store: caches {tuple(kcache.shape)}, {tuple(vcache.shape)} do not fit "
                           f"{nkv} kv heads of {d} and {dv}")
+    if rotary_dim:
+        require(cs, F32, "qkv_bias_norm_store.cs")
+        if rotary_dim % 2 or rotary_dim > d or tuple(cs.shape) != (N, rotary_dim // 2, 2):
+            raise KernelError(f"qkv_bias_norm_store: angles {tuple(cs.shape)} do not fit {N} tokens and a rotation "
+                              f"over {rotary_dim} of {d} values")
     q_out = torch.empty((N, nq, d), dtype=out_dtype, device=qkv.device)
     f = fn("layer_ops", "lumen_qkv_bias_norm_store",
            [P, c_int, c_longlong, P, P, P, c_float, P, P, P, c_int, P, P, P, c_int, c_int, c_int, c_int, c_int, c_int,
-            c_int, c_int, P])
+            c_int, c_int, P, c_int, c_int, c_float, P])
     check(f(ptr(qkv), S, N * width, ptr(bias), ptr(q_norm_w), ptr(k_norm_w), float(eps), ptr(cache_pos), ptr(tok_seq),
             ptr(block_table), block_table.stride(0), ptr(q_out), ptr(kcache), ptr(vcache), _is_bf16(q_out), N, nq * d,
-            nkv, d, dv, int(k_layout), int(v_layout), stream_ptr()), "qkv_bias_norm_store")
+            nkv, d, dv, int(k_layout), int(v_layout), ptr(cs) if rotary_dim else 0, int(rotary_dim),
+            0 if value_unit_eps is None else 1, float(value_unit_eps or 0.0), stream_ptr()), "qkv_bias_norm_store")
     return q_out
 
 
@@ -285,6 +295,184 @@ def attn_talk(q, kcache, vcache, block_table, tok_seq, tok_pos, talk, window, ke
     check(f(ptr(q), ptr(kcache), ptr(vcache), ptr(block_table), block_table.stride(0), ptr(tok_seq), ptr(tok_pos),
             ptr(talk), ptr(out), ptr(W), ptr(stats), ptr(parts), _is_bf16(q), N, rows_per_pass, row_stride, nq, nkv, d, dv,
             int(window), int(keep_first), float(scale), int(k_layout), int(v_layout), stream_ptr()), "attn_talk")
+    return out
+
+
+def conv_silu(u, c0, C, weight, bias, state, ctx_tok_seq, cu_q, seq_slot, n_seqs, decode):
+    """silu(bias + causal convolution over time) of columns c0 .. c0 + C - 1 of a projection that
+    arrives as partial sums u float32 [S, N, W] (or [N, W]); weight float32 [taps, C], the last
+    row the current token's; bias float32 [C] or None; state float32 [slots, taps - 1, C], the
+    sequences' last inputs (row seq_slot[b] is sequence b's), moved on to the step's end.
+    `decode`: every sequence brings exactly one token and row b is sequence b's. float32 [N, C]."""
+    u, S = _partials(u, "conv_silu.u")
+    _, N, W = u.shape
+    require(weight, F32, "conv_silu.weight")
+    taps = weight.shape[0]
+    if weight.shape[1] != C or c0 < 0 or c0 + C > W or not 1 <= taps <= 16:
+        raise KernelError(f"conv_silu: weight {tuple(weight.shape)} does not fit {C} of {W} columns (1 to 16 taps)")
+    stride = 0
+    if taps > 1:
+        if state is None or state.dtype != F32 or tuple(state.shape[1:]) != (taps - 1, C) or state.stride(2) != 1 \
+                or state.stride(1) != C:
+            raise KernelError(f"conv_silu: state must be float32 [slots, {taps - 1}, {C}] with dense rows")
+        stride = state.stride(0)
+    if bias is not None:
+        require(bias, F32, "conv_silu.bias")
+    for t, nm in ((ctx_tok_seq, "tok_seq"), (cu_q, "cu_q"), (seq_slot, "seq_slot")):
+        require(t, I32, f"conv_silu.{nm}")
+    out = torch.empty((N, C), dtype=F32, device=u.device)
+    f = fn("ssm", "lumen_conv_silu", [P, c_int, c_longlong, c_int, c_int, c_int, P, P, c_int, P, c_longlong, P, P, P,
+                                      c_int, c_int, P, c_int, P])
+    check(f(ptr(u), S, N * W, W, int(c0), int(C), ptr(weight), ptr(bias), taps, ptr(state) if taps > 1 else 0, stride,
+            ptr(ctx_tok_seq), ptr(cu_q), ptr(seq_slot), int(n_seqs), 1 if decode else 0, ptr(out), N, stream_ptr()),
+          "conv_silu")
+    return out
+
+
+def ssm_scan(xbc, heads, head_dim, state_size, groups, u, dt_col, dt_bias, a_log, d_skip, state, cu_q, seq_slot, n_seqs):
+    """The recurrence of a state-space mixer, per head h (group g = h // (heads / groups)):
+    S <- exp(-exp(a_log[h]) dt) S + dt B x^T, y = S^T C + d_skip[h] x, with dt = softplus(the
+    projection's column dt_col + h, summed over its partials, + dt_bias[h]). xbc float32
+    [N, heads * head_dim + 2 * groups * state_size] = (x, B, C); u float32 [S, N, W] or [N, W];
+    state float32 [slots, heads, state_size, head_dim], row seq_slot[b] sequence b's, updated in
+    place. Returns y float32 [N, heads * head_dim]."""
+    require(xbc, F32, "ssm_scan.xbc")
+    u, S = _partials(u, "ssm_scan.u")
+    _, N, W = u.shape
+    inner = heads * head_dim
+    if tuple(xbc.shape) != (N, inner + 2 * groups * state_size) or heads % groups:
+        raise KernelError(f"ssm_scan: xbc {tuple(xbc.shape)} does not fit {heads} heads of {head_dim}, "
+                          f"{groups} groups of {state_size}")
+    for t, nm in ((dt_bias, "dt_bias"), (a_log, "a_log"), (d_skip, "d_skip")):
+        require(t, F32, f"ssm_scan.{nm}")
+        if t.numel() != heads:
+            raise KernelError(f"ssm_scan: {nm} must have {heads} values")
+    require(state, F32, "ssm_scan.state", contiguous=False)
+    if tuple(state.shape[1:]) != (heads, state_size, head_dim) or not state[0].is_contiguous():
+        raise KernelError(f"ssm_scan: state must be float32 [slots, {heads}, {state_size}, {head_dim}]")
+    require(cu_q, I32, "ssm_scan.cu_q")
+    require(seq_slot, I32, "ssm_scan.seq_slot")
+    y = torch.empty((N, inner), dtype=F32, device=xbc.device)
+    f = fn("ssm", "lumen_ssm_scan", [P, c_int, c_int, c_int, c_int, P, c_int, c_longlong, c_int, c_int, P, P, P, P,
+                                     c_longlong, P, P, c_int, P, c_int, P])
+    check(f(ptr(xbc), heads, head_dim, state_size, groups, ptr(u), S, N * W, W, int(dt_col), ptr(dt_bias), ptr(a_log),
+            ptr(d_skip), ptr(state), state.stride(0), ptr(cu_q), ptr(seq_slot), int(n_seqs), ptr(y), N, stream_ptr()),
+          "ssm_scan")
+    return y
+
+
+def gated_part_norm(y, u, z_col, weight, eps, parts, out_dtype):
+    """v = y * silu(z) with z the columns z_col .. of the projection's partial sums u, then an RMS
+    norm of each of `parts` equal pieces of the row by its own root mean square, times weight.
+    y float32 [N, W]; weight float32 [W]; returns [N, W] in out_dtype."""
+    require(y, F32, "gated_part_norm.y")
+    require(weight, F32, "gated_part_norm.weight")
+    u, S = _partials(u, "gated_part_norm.u")
+    N, W = y.shape
+    if u.shape[1] != N or weight.numel() != W or parts < 1 or W % parts or z_col < 0 or z_col + W > u.shape[2]:
+        raise KernelError(f"gated_part_norm: rows of {W} in {parts} parts do not fit {tuple(u.shape)}")
+    out = torch.empty((N, W), dtype=out_dtype, device=y.device)
+    f = fn("ssm", "lumen_gated_part_norm", [P, P, c_int, c_longlong, c_int, c_int, P, c_float, c_int, c_int, P, c_int,
+                                            c_int, P])
+    check(f(ptr(y), ptr(u), S, N * u.shape[2], u.shape[2], int(z_col), ptr(weight), float(eps), W, int(parts), ptr(out),
+            _is_bf16(out), N, stream_ptr()), "gated_part_norm")
+    return out
+
+
+def xielu(z, act, out_dtype):
+    """x > 0: softplus(p) x^2 + x/2; x <= 0: (1/2 + softplus(q)) (e^x - 1 - x) + x/2, with
+    (p, q) = act float32 [2] on the device; z float32 [N, F] or [S, N, F] partials."""
+    z, S = _partials(z, "xielu.z")
+    require(act, F32, "xielu.act")
+    if act.numel() != 2:
+        raise KernelError("xielu: act holds two values")
+    _, N, Fw = z.shape
+    out = torch.empty((N, Fw), dtype=out_dtype, device=z.device)
+    f = fn("ssm", "lumen_xielu", [P, c_int, c_longlong, P, P, c_int, c_longlong, P])
+    check(f(ptr(z), S, N * Fw, ptr(act), ptr(out), _is_bf16(out), N * Fw, stream_ptr()), "xielu")
+    return out
+
+
+MOE_TILE_ROWS = None
+
+
+def moe_tile_rows() -> int:
+    global MOE_TILE_ROWS
+    if MOE_TILE_ROWS is None:
+        MOE_TILE_ROWS = int(int_fn("moe", "lumen_moe_tile_rows", [])())
+    return MOE_TILE_ROWS
+
+
+def moe_route(logits, correction, top, scale):
+    """Softmax over a token's router logits (float32 [N, E]), the `top` experts with the largest
+    score + correction (equal ones: the lower index), and their scores (without the correction)
+    times `scale` as weights. Returns (idx int32 [N, top], weights float32 [N, top])."""
+    require(logits, F32, "moe_route.logits")
+    N, E = logits.shape
+    if correction is not None:
+        require(correction, F32, "moe_route.correction")
+        if correction.numel() != E:
+            raise KernelError(f"moe_route: the correction must have {E} values")
+    idx = torch.empty((N, top), dtype=I32, device=logits.device)
+    wt = torch.empty((N, top), dtype=F32, device=logits.device)
+    f = fn("moe", "lumen_moe_route", [P, P, c_int, c_int, c_float, P, P, c_int, P])
+    check(f(ptr(logits), ptr(correction), E, int(top), float(scale), ptr(idx), ptr(wt), N, stream_ptr()), "moe_route")
+    return idx, wt
+
+
+def moe_group(idx, n_experts):
+    """The step's (token, choice) entries in order of their expert, and the row tiles the grouped
+    products walk; entries whose index is >= n_experts are left out. Returns (sorted int32
+    [entries], tiles int32 [max_tiles, 3], n_tiles int32 [1], max_tiles)."""
+    require(idx, I32, "moe_group.idx")
+    entries = idx.numel()
+    max_tiles = entries // moe_tile_rows() + min(int(n_experts), entries)
+    sorted_ = torch.empty((entries,), dtype=I32, device=idx.device)
+    tiles = torch.empty((max(max_tiles, 1), 3), dtype=I32, device=idx.device)
+    n_tiles = torch.empty((1,), dtype=I32, device=idx.device)
+    f = fn("moe", "lumen_moe_group", [P, c_int, c_int, P, P, P, P])
+    check(f(ptr(idx), entries, int(n_experts), ptr(sorted_), ptr(tiles), ptr(n_tiles), stream_ptr()), "moe_group")
+    return sorted_, tiles, n_tiles, max_tiles
+
+
+def moe_product(a, w, group, weights, top, n_tokens, gated):
+    """A grouped product over the tiles of moe_group. gated: a [tokens, K] in the run's type, w
+    [E, 2 F, K] (gate rows, then up rows) -> silu(gate) * up as [entries, F] in a's type. Not
+    gated: a [entries, K], w [E, D, K] -> float32 [top, tokens, D] with every entry's product
+    times its weight at [choice][token]; rows of entries that are left out (identity experts)
+    are not written."""
+    sorted_, tiles, n_tiles, max_tiles = group
+    E, rows, K = w.shape
+    if a.shape[1] != K or not a.is_contiguous() or not w.is_contiguous():
+        raise KernelError(f"moe_product: activations {tuple(a.shape)} do not fit weights {tuple(w.shape)}")
+    if gated:
+        if rows % 2:
+            raise KernelError("moe_product: gate and up rows come in equal numbers")
+        n_out = rows // 2
+        out = torch.empty((n_tokens * top, n_out), dtype=a.dtype, device=a.device)
+    else:
+        n_out = rows
+        require(weights, F32, "moe_product.weights")
+        out = torch.empty((top, n_tokens, n_out), dtype=F32, device=a.device)
+    f = fn("moe", "lumen_moe_product", [P, c_int, P, c_int, P, P, P, c_int, P, P, c_int, c_int, c_int, c_int, c_int, P])
+    check(f(ptr(a), _is_bf16(a), ptr(w), _is_bf16(w), ptr(sorted_), ptr(tiles), ptr(n_tiles), int(max_tiles),
+            ptr(weights), ptr(out), K, n_out, int(top), int(n_tokens), 1 if gated else 0, stream_ptr()), "moe_product")
+    return out
+
+
+def moe_identity(x, idx, weights, out, n_experts):
+    """out[choice][token][:] = weight * x[token][:] for the entries whose expert index is >=
+    n_experts (experts that hand their input on). x [N, D]; out float32 [top, N, D]."""
+    require(idx, I32, "moe_identity.idx")
+    require(weights, F32, "moe_identity.weights")
+    require(out, F32, "moe_identity.out")
+    N, D = x.shape
+    top = idx.shape[1]
+    if tuple(out.shape) != (top, N, D) or not x.is_contiguous():
+        raise KernelError(f"moe_identity: out {tuple(out.shape)} does not fit {top} choices of {N} rows of {D}")
+    f = fn("moe", "lumen_moe_identity", [P, c_int, P, P, P, c_int, c_int, c_int, c_int, P])
+    check(f(ptr(x), _is_bf16(x), ptr(idx), ptr(weights), ptr(out), int(n_experts), top, N, D, stream_ptr()),
+          "moe_identity")
     return out
 
 
@@ -426,24 +614,29 @@ def gemm_tc_qkv(x, w, q_norm_w, k_norm_w, eps, cs, rotary_dim, cache_pos, tok_se
 
 
 def attn_generic(q, kcache, vcache, block_table, tok_seq, tok_pos, window, scale,
-                 layout=LAYOUT_LINEAR):
-    """Causal attention of N query tokens over the paged cache. q [N, nq, d]."""
+                 layout=LAYOUT_LINEAR, v_layout=None):
+    """Causal attention of N query tokens over the paged cache. q [N, nq, d]; keys
+    [pages, nkv, PAGE, d]; values [pages, nkv, PAGE, dv] (dv may differ from d); returns
+    [N, nq, dv]. Scores and weights are float32 in either type."""
     N, nq, d = q.shape
     nkv = kcache.shape[1]
+    dv = vcache.shape[3]
+    v_layout = layout if v_layout is None else v_layout
     require(q, q.dtype, "attn.q")
     require(kcache, q.dtype, "attn.kcache")
     require(vcache, q.dtype, "attn.vcache")
     require(block_table, I32, "attn.block_table")
     require(tok_seq, I32, "attn.tok_seq")
     require(tok_pos, I32, "attn.tok_pos")
-    if d % 16 or d > 256:
-        raise KernelError(f"attention takes head sizes in steps of 16 up to 256, not {d}")
-    out = torch.empty_like(q)
+    if d > 256 or dv > 256 or kcache.shape[3] != d or tuple(vcache.shape[1:3]) != tuple(kcache.shape[1:3]):
+        raise KernelError(f"attention takes key and value sizes up to 256 and caches that fit them, not {d} / {dv} "
+                          f"with {tuple(kcache.shape)} / {tuple(vcache.shape)}")
+    out = torch.empty((N, nq, dv), dtype=q.dtype, device=q.device)
     f = fn("attn_generic", "lumen_attn_generic",
-           [P, P, P, P, c_int, P, P, P, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_int, P])
+           [P, P, P, P, c_int, P, P, P, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_int, P])
     check(f(ptr(q), ptr(kcache), ptr(vcache), ptr(block_table), block_table.stride(0), ptr(tok_seq),
-            ptr(tok_pos), ptr(out), _is_bf16(q), N, nq, nkv, d, int(window), float(scale), int(layout),
-            stream_ptr()), "attn_generic")
+            ptr(tok_pos), ptr(out), _is_bf16(q), N, nq, nkv, d, dv, int(window), float(scale), int(layout),
+            int(v_layout), stream_ptr()), "attn_generic")
     return out
 
 

@@ -1,4 +1,8 @@
-"""The attention mixer: grouped-query causal attention over the cache.
+"""The attention mixers: grouped-query causal attention over the cache.
+
+"gqa_attention" (GQAttention) norms each head, "wide_norm_attention" (WideNormAttention, at
+the end of this file) norms a whole projection at once, has biases, a value norm and values of
+their own width; both hand their queries to `causal_attention`, which picks the kernel.
 
 In order (crates/aegisllm-cuda/src/executor/attention.rs:139-202,241-250,341-352,
 413-425; prompt twin executor/prefill/layer.rs:472-636,810-823,967-1047):
@@ -120,18 +124,91 @@ class GQAttention:
         return self.o(out.view(-1, self.nq * self.d), split_ok=True, add_to=residual)
 
     def attend(self, q, kc, vc, table, ctx, layout):
-        """Chooses the kernel by the step's shape: the split-KV kernel when every sequence
-        brings one token, the flash kernel for prompts, and the general kernel for the
-        32-bit path and for head sizes the fast kernels do not take. All agree within rounding."""
-        fast = (layout == K.LAYOUT_SW128 and q.dtype == torch.bfloat16 and self.d in (64, 128)
-                and self.nq // self.nkv <= 16)
-        if fast and ctx.is_decode:
-            return K.attn_decode(q, kc, vc, table, ctx.cache_pos, self.window, self.scale)
-        if fast:
-            # a captured step is replayed for other divisions of its tokens than the one it was
-            # captured with: the kernel then takes the division from the device alone
-            q_lens = None if ctx.extras.get("captured") else ctx.q_lens
-            return K.attn_prefill(q, kc, vc, table, ctx.cu_q, ctx.seq_start, q_lens, self.window,
-                                  self.scale, n_seqs=ctx.B)
-        return K.attn_generic(q, kc, vc, table, ctx.tok_seq, ctx.cache_pos, self.window, self.scale,
-                              layout=layout)
+        return causal_attention(q, kc, vc, table, ctx, layout, layout, self.window, self.scale)
+
+
+def causal_attention(q, kc, vc, table, ctx, k_layout, v_layout, window, scale):
+    """Chooses the kernel by the step's shape: the split-KV kernel when every sequence
+    brings one token, the flash kernel for prompts, and the general kernel for the
+    32-bit path and for head sizes the fast kernels do not take (keys and values of
+    different widths among them). All agree within rounding. q [N, nq, d]."""
+    nq, d = q.shape[1], q.shape[2]
+    nkv, dv = kc.shape[1], vc.shape[3]
+    fast = (k_layout == K.LAYOUT_SW128 and v_layout == K.LAYOUT_SW128 and q.dtype == torch.bfloat16
+            and d == dv and d in (64, 128) and nq // nkv <= 16)
+    if fast and ctx.is_decode:
+        return K.attn_decode(q, kc, vc, table, ctx.cache_pos, window, scale)
+    if fast:
+        # a captured step is replayed for other divisions of its tokens than the one it was
+        # captured with: the kernel then takes the division from the device alone
+        q_lens = None if ctx.extras.get("captured") else ctx.q_lens
+        return K.attn_prefill(q, kc, vc, table, ctx.cu_q, ctx.seq_start, q_lens, window, scale, n_seqs=ctx.B)
+    return K.attn_generic(q, kc, vc, table, ctx.tok_seq, ctx.cache_pos, window, scale, layout=k_layout,
+                          v_layout=v_layout)
+
+
+@register_part("mixer", "wide_norm_attention")
+class WideNormAttention:
+    """q, k, v = y Wq^T + bq, y Wk^T + bk, y Wv^T + bv; ONE RMS norm over the whole query
+    projection (all heads at once, a weight of heads x dim values) and one over the whole key
+    projection; then the position part's rotation of the first `rotary_dim` values of every
+    query and key head; every value head divided by its own root mean square (no weight) and
+    cached so; a query at position p sees key j if 0 <= p - j < window (window 0: every earlier
+    key); ordinary softmax of scale * q . k; query head h reads kv head h // (heads / kv_heads);
+    o = ctx Wo^T, without a bias. Keys are `head_dim` wide, values `value_dim`. Norms, angles,
+    scores and weights are float32. Parameters: hidden_size, num_heads, num_kv_heads, head_dim,
+    value_dim, softmax_scale, window, norm_eps, value_norm (bool), position (a PartSpec)."""
+    graph_safe = True
+
+    @classmethod
+    def tensors(cls, spec):
+        p = spec.params
+        D, H, G, d, dv = (int(need(p, k, "wide_norm_attention")) for k in
+                          ("hidden_size", "num_heads", "num_kv_heads", "head_dim", "value_dim"))
+        pre = spec.prefix
+        t = {f"{pre}.q": ((H * d, D), "matrix"), f"{pre}.q.b": ((H * d,), "matrix"),
+             f"{pre}.k": ((G * d, D), "matrix"), f"{pre}.k.b": ((G * d,), "matrix"),
+             f"{pre}.v": ((G * dv, D), "matrix"), f"{pre}.v.b": ((G * dv,), "matrix"),
+             f"{pre}.q.norm": ((H * d,), "norm"), f"{pre}.k.norm": ((G * d,), "norm"),
+             f"{pre}.o": ((D, H * dv), "matrix")}
+        t.update(part_tensors("position", p["position"]))
+        return t
+
+    def __init__(self, spec, weights, runtime):
+        p = spec.params
+        self.runtime = runtime
+        self.H, self.G = int(p["num_heads"]), int(p["num_kv_heads"])
+        self.d, self.dv = int(p["head_dim"]), int(p["value_dim"])
+        if self.H % self.G:
+            raise ValueError(f"{self.H} heads are not a multiple of {self.G} kv heads")
+        if self.d > 256 or self.dv > 256:
+            raise ValueError(f"key size {self.d}, value size {self.dv}: the attention kernels take up to 256")
+        self.window = int(p.get("window", 0) or 0)
+        self.scale = float(need(p, "softmax_scale", "wide_norm_attention"))
+        self.eps = float(need(p, "norm_eps", "wide_norm_attention"))
+        self.value_norm = bool(p.get("value_norm", False))
+        self.position = build_part("position", p["position"], weights, runtime)
+        pre = spec.prefix
+        f32 = lambda n: weights[n].to(device=runtime.device, dtype=torch.float32).contiguous()
+        self.qkv = Linear.stacked([weights[f"{pre}.q"], weights[f"{pre}.k"], weights[f"{pre}.v"]], runtime)
+        self.qkv_bias = torch.cat([f32(f"{pre}.q.b"), f32(f"{pre}.k.b"), f32(f"{pre}.v.b")]).contiguous()
+        self.q_norm, self.k_norm = f32(f"{pre}.q.norm"), f32(f"{pre}.k.norm")
+        self.o = Linear(weights[f"{pre}.o"], runtime)
+
+    def cache_need(self):
+        return CacheNeed(self.G, self.d, self.window, v_dim=0 if self.dv == self.d else self.dv)
+
+    def state_shape(self):
+        return None
+
+    def forward(self, y, ctx, entry):
+        kc, vc, table = entry.cache()
+        qkv = self.qkv(y, split_ok=True)
+        rot = self.position.rotary_dim
+        q = K.qkv_bias_norm_store(qkv, self.qkv_bias, self.q_norm, self.k_norm, self.eps, ctx.cache_pos,
+                                  ctx.tok_seq, table, kc, vc, self.H, self.G, self.d, self.dv, self.runtime.dtype,
+                                  k_layout=entry.layout, v_layout=entry.v_layout,
+                                  cs=self.position.angles(ctx) if rot else None, rotary_dim=rot,
+                                  value_unit_eps=self.eps if self.value_norm else None)
+        out = causal_attention(q, kc, vc, table, ctx, entry.layout, entry.v_layout, self.window, self.scale)
+        return self.o(out.view(-1, self.H * self.dv), split_ok=True)

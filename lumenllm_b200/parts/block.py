@@ -6,6 +6,10 @@ The adds are not done here: a block hands its last update on as `pending`, and
 the next norm (the next block's, or the model's final one) adds it while it
 reads the stream anyway.
 
+"parallel": h' = h + (mixer(norm(h)) + ffn(norm(h))): ONE norm, whose output both sublayers
+read; a layer may lack the feed-forward. The two updates go on side by side as one stack of
+partial sums.
+
 "sandwich_conv": r = h + norm_b(mixer(conv(norm_a(h)))); h' = r + norm_d(ffn(conv(norm_c(r)))):
 a norm before and after each sublayer, and a short causal convolution over time of what each
 sublayer reads (parts/conv.py), whose last inputs are the block's per-sequence state. The second
@@ -107,3 +111,34 @@ class SandwichConvBlock:
                                        ctx, self.runtime.dtype)
         m = self.ffn.forward(x, ctx)
         return h, NormedUpdate(m, self.norm_ffn_out.weight, self.norm_ffn_out.eps)
+
+
+@register_part("block", "parallel")
+class ParallelBlock:
+    @classmethod
+    def tensors(cls, layer_spec):
+        t = {}
+        t.update(part_tensors("norm", layer_spec.norms["input"]))
+        t.update(part_tensors("mixer", layer_spec.mixer))
+        if layer_spec.ffn is not None:
+            t.update(part_tensors("ffn", layer_spec.ffn))
+        return t
+
+    def __init__(self, layer_spec, weights, runtime):
+        self.runtime = runtime
+        self.norm = build_part("norm", layer_spec.norms["input"], weights, runtime)
+        self.mixer = build_part("mixer", layer_spec.mixer, weights, runtime)
+        self.ffn = build_part("ffn", layer_spec.ffn, weights, runtime) if layer_spec.ffn is not None else None
+
+    @property
+    def graph_safe(self):
+        return all(getattr(p, "graph_safe", False) for p in [self.mixer] + ([self.ffn] if self.ffn else []))
+
+    def forward(self, h, pending, ctx, entry):
+        y = self.norm.forward(h, pending, self.runtime.dtype)
+        a = self.mixer.forward(y, ctx, entry)
+        if self.ffn is None:
+            return h, a
+        m = self.ffn.forward(y, ctx)
+        stack = lambda d: d if d.dim() == 3 else d.unsqueeze(0)
+        return h, torch.cat([stack(a), stack(m)], dim=0)

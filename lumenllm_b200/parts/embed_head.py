@@ -60,15 +60,15 @@ class LinearHead:
         if not spec.params.get("own_tensor", True):        # the head IS the tied table: no tensor of its own
             return {}
         shape = (int(need(spec.params, "vocab_size", "head")), int(need(spec.params, "hidden_size", "head")))
-        return {f"{spec.prefix}.weight": (shape, "optional" if spec.params.get("tied_to") else "matrix")}
+        return {tensor_name(spec): (shape, "optional" if spec.params.get("tied_to") else "matrix")}
 
     @classmethod
     def fallbacks(cls, spec):
         other = spec.params.get("falls_back_to")
-        return {f"{spec.prefix}.weight": other} if other and not spec.params.get("tied_to") else {}
+        return {tensor_name(spec): other} if other and not spec.params.get("tied_to") else {}
 
     def __init__(self, spec, weights, runtime):
-        own = f"{spec.prefix}.weight"
+        own = tensor_name(spec)
         name = own if spec.params.get("own_tensor", True) and own in weights else spec.params.get("tied_to")
         if name is None or name not in weights:
             raise KeyError(f"the output head needs '{own}'")

@@ -12,6 +12,17 @@ and a small kernel adds them and applies the activation.
 taken element by element, N divides a token's vector by its root mean square
 (sqrt(mean(v^2) + eps)), and (a, b, c, e) are the four values of the tensor `<prefix>.act`.
 The activation is one float32 kernel over the product's partial sums.
+
+"xielu_mlp": u = y Wu^T, out = xIELU(u) Wd^T with xIELU(z) = softplus(p) z^2 + z/2 for z > 0 and
+(1/2 + softplus(q)) (e^z - 1 - z) + z/2 for z <= 0, (p, q) the two values of `<prefix>.act`.
+
+"routed_experts": many small SwiGLU experts (`<prefix>.e<i>.gate/up/down`, no biases) of which
+each token uses `top`. The router's logits y Wr^T are float32; s = softmax over ALL router
+outputs; the `top` outputs with the largest s + correction are chosen, and each counts with its
+s (without the correction) times `scale`, not renormalised. The last `identity` router outputs
+are experts without tensors that hand their input on. A shared expert (`<prefix>.shared`), when
+the model has one, runs for every token and is added. The update goes on as partial sums: one
+for each of a token's choices, then the shared expert's.
 """
 from __future__ import annotations
 
@@ -27,19 +38,26 @@ from .linear import Linear
 class SwiGLU:
     graph_safe = True
 
+    @staticmethod
+    def names(spec):
+        """The three tensors' names; `tensor_names` = {"gate": suffix, "up": ..., "down": ...}
+        replaces the usual `.gate_proj.weight` and so on."""
+        sfx = spec.params.get("tensor_names") or {"gate": ".gate_proj.weight", "up": ".up_proj.weight",
+                                                  "down": ".down_proj.weight"}
+        return tuple(spec.prefix + sfx[k] for k in ("gate", "up", "down"))
+
     @classmethod
     def tensors(cls, spec):
         H = int(need(spec.params, "hidden_size", "swiglu"))
         I = int(need(spec.params, "intermediate_size", "swiglu"))
-        return {f"{spec.prefix}.gate_proj.weight": ((I, H), "matrix"),
-                f"{spec.prefix}.up_proj.weight": ((I, H), "matrix"),
-                f"{spec.prefix}.down_proj.weight": ((H, I), "matrix")}
+        gate, up, down = cls.names(spec)
+        return {gate: ((I, H), "matrix"), up: ((I, H), "matrix"), down: ((H, I), "matrix")}
 
     def __init__(self, spec, weights, runtime):
         self.runtime = runtime
-        pre = spec.prefix
-        g, u = weights[f"{pre}.gate_proj.weight"], weights[f"{pre}.up_proj.weight"]
-        self.down = Linear(weights[f"{pre}.down_proj.weight"], runtime)
+        gate, up, down = self.names(spec)
+        g, u = weights[gate], weights[up]
+        self.down = Linear(weights[down], runtime)
         self.interleaved = (not runtime.is_f32 and g.dtype == torch.bfloat16
                             and u.dtype == torch.bfloat16)
         if self.interleaved:
@@ -82,3 +100,90 @@ class PolyNormMLP:
         u = self.up(y, split_ok=True)                       # float32 [N, I], possibly S partials
         z = K.polynorm(u, self.act, self.eps, self.runtime.dtype)
         return self.down(z, split_ok=True)
+
+
+@register_part("ffn", "xielu_mlp")
+class XieluMLP:
+    graph_safe = True
+
+    @classmethod
+    def tensors(cls, spec):
+        H = int(need(spec.params, "hidden_size", "xielu_mlp"))
+        I = int(need(spec.params, "intermediate_size", "xielu_mlp"))
+        return {f"{spec.prefix}.up": ((I, H), "matrix"), f"{spec.prefix}.down": ((H, I), "matrix"),
+                f"{spec.prefix}.act": ((2,), "matrix")}
+
+    def __init__(self, spec, weights, runtime):
+        self.runtime = runtime
+        self.up = Linear(weights[f"{spec.prefix}.up"], runtime)
+        self.down = Linear(weights[f"{spec.prefix}.down"], runtime)
+        self.act = weights[f"{spec.prefix}.act"].to(device=runtime.device, dtype=torch.float32).contiguous()
+
+    def forward(self, y, ctx):
+        u = self.up(y, split_ok=True)                       # float32 [N, I], possibly S partials
+        return self.down(K.xielu(u, self.act, self.runtime.dtype), split_ok=True)
+
+
+@register_part("ffn", "routed_experts")
+class RoutedExperts:
+    """Parameters: hidden_size, expert_size, num_experts (with tensors), identity_experts,
+    top, scale, shared_size (0 or absent: no shared expert)."""
+    graph_safe = True
+
+    @staticmethod
+    def _sizes(p):
+        D, F, E, top = (int(need(p, k, "routed_experts")) for k in ("hidden_size", "expert_size", "num_experts", "top"))
+        return D, F, E, int(p.get("identity_experts", 0)), top, int(p.get("shared_size", 0) or 0)
+
+    @classmethod
+    def _shared_spec(cls, spec):
+        from ..config.spec import PartSpec
+        D, _, _, _, _, Fs = cls._sizes(spec.params)
+        return PartSpec("swiglu", {"hidden_size": D, "intermediate_size": Fs,
+                                   "tensor_names": {"gate": ".gate", "up": ".up", "down": ".down"}},
+                        prefix=f"{spec.prefix}.shared")
+
+    @classmethod
+    def tensors(cls, spec):
+        D, F, E, ident, _, Fs = cls._sizes(spec.params)
+        pre = spec.prefix
+        t = {f"{pre}.router": ((E + ident, D), "matrix"), f"{pre}.correction": ((E + ident,), "matrix")}
+        for e in range(E):
+            t.update({f"{pre}.e{e}.gate": ((F, D), "matrix"), f"{pre}.e{e}.up": ((F, D), "matrix"),
+                      f"{pre}.e{e}.down": ((D, F), "matrix")})
+        if Fs:
+            t.update(SwiGLU.tensors(cls._shared_spec(spec)))
+        return t
+
+    def __init__(self, spec, weights, runtime):
+        p = spec.params
+        self.runtime = runtime
+        self.D, self.F, self.E, self.ident, self.top, Fs = self._sizes(p)
+        if not 1 <= self.top <= self.E + self.ident:
+            raise ValueError(f"{self.top} choices among {self.E + self.ident} experts")
+        self.scale = float(need(p, "scale", "routed_experts"))
+        pre = spec.prefix
+        dev = runtime.device
+        # the router is multiplied in true 32-bit whatever the run's type
+        self.router = Linear(weights[f"{pre}.router"].to(device=dev, dtype=torch.float32), runtime)
+        self.correction = weights[f"{pre}.correction"].to(device=dev, dtype=torch.float32).contiguous()
+        wdt = torch.float32 if runtime.is_f32 else None
+        stack = lambda names: torch.stack([weights[n] if wdt is None else weights[n].to(wdt) for n in names]).contiguous()
+        gate = stack([f"{pre}.e{e}.gate" for e in range(self.E)])
+        up = stack([f"{pre}.e{e}.up" for e in range(self.E)])
+        self.w_gate_up = torch.cat([gate, up], dim=1).contiguous()          # [E, 2 F, D]: gate rows, then up rows
+        self.w_down = stack([f"{pre}.e{e}.down" for e in range(self.E)])    # [E, D, F]
+        self.shared = SwiGLU(self._shared_spec(spec), weights, runtime) if Fs else None
+
+    def forward(self, y, ctx):
+        N = y.shape[0]
+        idx, wt = K.moe_route(self.router(y), self.correction, self.top, self.scale)
+        group = K.moe_group(idx, self.E)
+        z = K.moe_product(y, self.w_gate_up, group, None, self.top, N, gated=True)
+        out = K.moe_product(z, self.w_down, group, wt, self.top, N, gated=False)      # [top, N, D]
+        if self.ident:
+            K.moe_identity(y, idx, wt, out, self.E)
+        if self.shared is None:
+            return out
+        s = self.shared.forward(y, ctx)
+        return torch.cat([out, s if s.dim() == 3 else s.unsqueeze(0)], dim=0)

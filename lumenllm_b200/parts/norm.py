@@ -4,7 +4,8 @@ y_i = x_i * 1/sqrt(mean(x^2) + eps) * w_i, everything in float32
 (crates/aegisllm-cuda/src/cuda/kernels/blackwell/norm_rope_kv.cu:36-62;
 crates/aegisllm-cpu/src/cpu/math.rs:4-8). `weight_offset` 1 gives the (1 + w)
 form that the reference folds in for other families (executor/loader.rs:189-194);
-it is a parameter, 0 for Qwen3 dense.
+it is a parameter, 0 for Qwen3 dense. With `scalar` the stored weight is ONE number
+(a tensor without dimensions) that multiplies every coordinate.
 """
 from __future__ import annotations
 
@@ -29,13 +30,16 @@ class NormedUpdate:
 class RMSNorm:
     @classmethod
     def tensors(cls, spec):
-        return {tensor_name(spec): ((need(spec.params, "size", "rmsnorm"),), "norm")}
+        size = need(spec.params, "size", "rmsnorm")
+        return {tensor_name(spec): (() if spec.params.get("scalar") else (size,), "norm")}
 
     def __init__(self, spec, weights, runtime):
         p = spec.params
         self.size = int(need(p, "size", "rmsnorm"))
         self.eps = float(need(p, "eps", "rmsnorm"))
         w = weights[tensor_name(spec)].to(device=runtime.device, dtype=torch.float32)
+        if p.get("scalar"):
+            w = w.reshape(1).expand(self.size)        # the kernels read one weight a coordinate
         off = float(p.get("weight_offset", 0.0))
         self.weight = (w + off).contiguous() if off else w.contiguous()
 

@@ -26,6 +26,9 @@ class Rotary:
         self.head_dim = int(need(p, "head_dim", "rotary"))
         self.rotary_dim = int(p.get("rotary_dim", self.head_dim))
         self.theta = float(need(p, "theta", "rotary"))
+        # `wide_frequencies`: theta^(-2i/rot) taken in 64-bit and rounded once to float32,
+        # instead of the float32 power and reciprocal above
+        self.wide = bool(p.get("wide_frequencies", False))
         if self.rotary_dim % 2 or not 0 < self.rotary_dim <= self.head_dim:
             raise ValueError(f"rotary_dim {self.rotary_dim} must be even and within head_dim")
         self.inv_freq = self.frequencies().to(runtime.device).contiguous()
@@ -34,7 +37,7 @@ class Rotary:
         """(cos, sin) for every token of the step, float32 [N, rot/2, 2]; made once per step
         and shared by all layers whose encoding has the same frequencies."""
         shared = ctx.extras.setdefault("per_step", {})   # emptied when the step's forward begins
-        key = ("rope", self.rotary_dim, self.theta)
+        key = ("rope", self.rotary_dim, self.theta, self.wide)
         cs = shared.get(key)
         if cs is None:
             from ..ops import kernels as K
@@ -42,6 +45,9 @@ class Rotary:
         return cs
 
     def frequencies(self) -> torch.Tensor:
+        if self.wide:
+            i2 = torch.arange(0, self.rotary_dim, 2, dtype=torch.float64)
+            return (torch.tensor(self.theta, dtype=torch.float64) ** (-i2 / self.rotary_dim)).to(torch.float32)
         i2 = torch.arange(0, self.rotary_dim, 2, dtype=torch.float32)
         return 1.0 / (torch.tensor(self.theta, dtype=torch.float32) ** (i2 / self.rotary_dim))
 
