@@ -111,7 +111,8 @@ def write_file(path, tensors: Dict[str, torch.Tensor], metadata=None) -> None:
         t = t.detach().cpu().contiguous()
         if t.dtype not in _NAMES:
             raise SafetensorsError(f"cannot store dtype {t.dtype}")
-        raw = t.view(torch.uint8).reshape(-1).numpy().tobytes() if t.numel() else b""
+        # a tensor without dimensions (one number) is stored with the shape [] and its bytes
+        raw = t.reshape(-1).view(torch.uint8).numpy().tobytes() if t.numel() else b""
         header[name] = {"dtype": _NAMES[t.dtype], "shape": list(t.shape),
                         "data_offsets": [offset, offset + len(raw)]}
         offset += len(raw)

@@ -96,14 +96,16 @@ def attention(h, w, pre, m, eps):
     q = unit(q, eps) * w[f"{pre}.q.norm"]              # over the whole projection, all heads at once
     k = unit(k, eps) * w[f"{pre}.k.norm"]
     q, k, v = q.view(T, H, d), k.view(T, G, d), v.view(T, G, dv)
-    pos = torch.arange(T)
-    q = rotate(q, pos, m["rot"]["base"], m["rot"]["dims"])
-    k = rotate(k, pos, m["rot"]["base"], m["rot"]["dims"])
+    if m.get("rot") is not None and m["rot"]["dims"]:
+        pos = torch.arange(T)
+        q = rotate(q, pos, m["rot"]["base"], m["rot"]["dims"])
+        k = rotate(k, pos, m["rot"]["base"], m["rot"]["dims"])
     v = unit(v, eps)                                   # each head's value by its own root mean square
     rep = H // G
     k, v = k.repeat_interleave(rep, dim=1), v.repeat_interleave(rep, dim=1)
     s = torch.einsum("ihe,jhe->hij", q, k) * m["scale"]
-    s = s.masked_fill(~window_mask(T, m["mask"]["size"])[None], float("-inf"))
+    size = m["mask"]["size"] if m.get("mask") is not None else T          # no mask: every earlier key
+    s = s.masked_fill(~window_mask(T, size)[None], float("-inf"))
     p = torch.softmax(s, dim=-1)
     o = torch.einsum("hij,jhe->ihe", p, v).reshape(T, H * dv)
     return o @ w[f"{pre}.o"].T
@@ -135,13 +137,12 @@ def state_space(h, w, pre, m, eps):
     dt = softplus(dt + w[f"{pre}.dt_bias"])                   # [T, H]
     decay = torch.exp(-torch.exp(w[f"{pre}.A_log"]) * dt)       # [T, H]
     per = H // G
+    Bh, Ch = B.repeat_interleave(per, dim=1), C.repeat_interleave(per, dim=1)   # head h reads group h // per
     y = torch.zeros(T, H, P, dtype=h.dtype)
-    for hd in range(H):
-        g = hd // per
-        S = torch.zeros(N, P, dtype=h.dtype)
-        for t in range(T):
-            S = decay[t, hd] * S + dt[t, hd] * torch.outer(B[t, g], x[t, hd])
-            y[t, hd] = S.T @ C[t, g] + w[f"{pre}.D"][hd] * x[t, hd]
+    S = torch.zeros(H, N, P, dtype=h.dtype)
+    for t in range(T):                                        # all heads at once, one token at a time
+        S = decay[t, :, None, None] * S + dt[t, :, None, None] * Bh[t, :, :, None] * x[t, :, None, :]
+        y[t] = torch.einsum("hnp,hn->hp", S, Ch[t]) + w[f"{pre}.D"][:, None] * x[t]
     y = y.reshape(T, inner) * silu(z)                          # the gate comes before the norm
     parts = m["norm_groups"]
     y = unit(y.view(T, parts, inner // parts), eps).reshape(T, inner) * w[f"{pre}.norm"]
@@ -164,7 +165,7 @@ def route(h, w, pre, r):
     identity experts."""
     s = torch.softmax(h @ w[f"{pre}.router"].T, dim=-1)
     idx = torch.topk(s + w[f"{pre}.correction"], r["top"], dim=-1).indices
-    return idx, torch.gather(s, 1, idx) * r["scale"]
+    return idx, torch.gather(s, 1, idx) * r.get("scale", 1.0)
 
 
 def expert_mixture(h, w, pre, mlp):
@@ -207,3 +208,11 @@ def forward(cfg, w, tokens, return_layers=False):
         after.append(x)
     logits = scalar_norm(x, w["final.norm"], eps) @ w["head"].T
     return (logits, torch.stack(after)) if return_layers else logits
+
+
+def generate_greedy(cfg, w, prompt, n):
+    toks, out = list(prompt), []
+    for _ in range(n):
+        out.append(int(forward(cfg, w, toks)[-1].argmax()))
+        toks.append(out[-1])
+    return out
