@@ -7,12 +7,12 @@ HBM roofline of the decode step.
 
     python bench.py [--gpus 1] [--steps K] [--warmup W] [--impl ours|reference]
                     [--shape 8b|14b|32b] [--timings]
-    python bench.py --design dabevik [--sizes 2k,4k] [--batch B] [--steps K] [--warmup W]
+    python bench.py --design dabevik|rasezen [--sizes 2k,4k] [--batch B] [--steps K] [--warmup W]
 
 `--shape` runs the same measurement at the two larger workloads (their batch, prompt
 lengths, context and sampling); `--timings` adds, from a separate pass that is not
 timed as a whole, each kernel class's share of a decode step and of a prompt step.
-`--design dabevik` measures that design beside the Qwen3 decoder at equal sizes instead (a few
+`--design dabevik` (or `rasezen`) measures that design beside the Qwen3 decoder at equal sizes instead (a few
 layers of real-model size, random weights: prompt and decode tokens per second, and each class
 of kernels' time in a step of either kind; lumenllm_b200/compare.py). The default workload and
 its JSON line are not touched by it.
@@ -318,16 +318,16 @@ def design_main(args) -> int:
         return 2
     from lumenllm_b200 import compare
     sizes = [x.strip() for x in args.sizes.split(",") if x.strip()]
-    unknown = [x for x in sizes if x not in compare.SIZES]
+    unknown = [x for x in sizes if x not in compare.sizes_of(args.design)]
     if unknown:
-        print(f"bench.py: unknown sizes {unknown}; known: {sorted(compare.SIZES)}", file=sys.stderr)
+        print(f"bench.py: unknown sizes {unknown}; known: {sorted(compare.sizes_of(args.design))}", file=sys.stderr)
         return 2
     clocks = Clocks()
     clocks.start()
     rows = compare.run(args.design, sizes, args.batch or 8, max(1, args.steps), max(3, args.warmup))
     time.sleep(0.3)
     clocks.stop()
-    windows = [rows[n][m].pop("window") for n in rows for m in ("dabevik", "qwen3")]
+    windows = [rows[n][m].pop("window") for n in rows for m in (args.design, "qwen3")]
     pk = peaks()
     print(json.dumps({"metric": "design_comparison", "design": args.design, "against": "qwen3", "dtype": "bf16",
                       "data": "synthetic", "weights": "random N(0,0.02)", "n_gpus": 1, "steps": max(1, args.steps),
@@ -357,7 +357,7 @@ def main() -> int:
                     help="context length (default: the workload's)")
     ap.add_argument("--prompt-len", default=None, metavar="LO:HI",
                     help="prompt lengths are drawn uniformly from this range")
-    ap.add_argument("--design", default=None, choices=["dabevik"],
+    ap.add_argument("--design", default=None, choices=["dabevik", "rasezen"],
                     help="measure this design beside the Qwen3 decoder at equal sizes instead of the benchmark")
     ap.add_argument("--sizes", default="2k,4k", help="with --design: which of compare.SIZES to run")
     args = ap.parse_args()

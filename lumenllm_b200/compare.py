@@ -1,4 +1,4 @@
-"""Dabevik beside the closest other model of the library (the Qwen3 dense decoder) at equal
+"""Dabevik, or Rasezen, beside the closest other model of the library (the Qwen3 dense decoder) at equal
 sizes: prompt and decode throughput of a few layers of real-model size with random weights, and
 what each class of kernels takes of a step. `python bench.py --design dabevik` prints the result
 as one JSON line.
@@ -8,6 +8,12 @@ and window (every layer of the Qwen3 twin slides the same window). What differs 
 two feed-forward matrices instead of three, biased projections, norms on both sides of a
 sublayer, the convolutions of the sublayers' inputs, learned positions instead of rotation, kept
 first tokens, and the mix of the heads' weights.
+
+Rasezen (`--design rasezen`, RASEZEN_SIZES): the same width, layers, vocabulary, attention heads,
+kv heads, head size, window and dense feed-forward width; what differs is the design: parallel
+blocks with one norm a layer, norms over whole projections, a value norm, some layers whose
+mixer is a state-space recurrence instead of attention, and feed-forwards that are mixtures of
+small experts (their chosen experts and the shared one together about a dense one's size).
 """
 from __future__ import annotations
 
@@ -19,6 +25,17 @@ SIZES = {
                vocab=32768, taps=4),
     "4k": dict(width=4096, heads=32, kv_heads=8, dim=128, ff=12288, window=2048, keep_first=4, layers=4,
                vocab=32768, taps=4),
+}
+# Rasezen: layers as (mixer, feed-forward) pairs, "a" attention, "s" state-space; "d" dense, "e" experts
+RASEZEN_SIZES = {
+    "2k": dict(width=2048, heads=16, kv_heads=4, dim=128, ff=8192, window=1024, vocab=32768,
+               ssm=dict(heads=64, vdim=64, state=128, groups=8, conv=4, norm_groups=8),
+               moe=dict(ff=1024, experts=16, identity=2, top=4, scale=2.5, shared=2048),
+               pattern=["ad", "se", "ae", "ae", "se", "ae", "ad", "se"]),
+    "4k": dict(width=4096, heads=32, kv_heads=8, dim=128, ff=12288, window=2048, vocab=32768,
+               ssm=dict(heads=128, vdim=64, state=128, groups=8, conv=4, norm_groups=8),
+               moe=dict(ff=1536, experts=16, identity=2, top=4, scale=2.5, shared=3072),
+               pattern=["ad", "se", "ae", "se"]),
 }
 CONTEXT = 4096
 PROMPT_TOKENS = 2048
@@ -34,12 +51,25 @@ def dabevik_config(s):
                        for _ in range(s["layers"])]}
 
 
+def rasezen_config(s):
+    attn = {"heads": s["heads"], "kv_heads": s["kv_heads"], "dim": s["dim"], "vdim": s["dim"],
+            "scale": s["dim"] ** -0.5, "mask": {"size": s["window"]}, "rot": {"base": 1000000.0, "dims": s["dim"]}}
+    m = s["moe"]
+    experts = {"kind": "moe", "expert": {"ff": m["ff"]}, "shared": {"ff": m["shared"]},
+               "router": {"experts": m["experts"], "identity": m["identity"], "scale": m["scale"], "top": m["top"]}}
+    layers = [{"type": "attention" if p[0] == "a" else "mamba2", "mixer": attn if p[0] == "a" else dict(s["ssm"]),
+               "mlp": {"kind": "dense", "ff": s["ff"]} if p[1] == "d" else experts} for p in s["pattern"]]
+    return {"architecture": "Rasezen", "vocab": s["vocab"], "width": s["width"], "norm": {"eps": 1e-6},
+            "max_positions": CONTEXT, "layers": layers}
+
+
 def qwen3_config(s):
+    n_layers = s["layers"] if "layers" in s else len(s["pattern"])
     return dict(architectures=["Qwen3ForCausalLM"], model_type="qwen3", hidden_size=s["width"],
-                num_hidden_layers=s["layers"], num_attention_heads=s["heads"], num_key_value_heads=s["kv_heads"],
+                num_hidden_layers=n_layers, num_attention_heads=s["heads"], num_key_value_heads=s["kv_heads"],
                 head_dim=s["dim"], intermediate_size=s["ff"], vocab_size=s["vocab"], rope_theta=1000000.0,
                 rms_norm_eps=1e-6, max_position_embeddings=CONTEXT, tie_word_embeddings=True,
-                sliding_window=s["window"], layer_types=["sliding_attention"] * s["layers"])
+                sliding_window=s["window"], layer_types=["sliding_attention"] * n_layers)
 
 
 # kernel entry point -> class of kernels, for both designs
@@ -52,6 +82,10 @@ CLASSES = {
     "lumen_attn_prefill": "attention", "lumen_attn_generic": "attention", "lumen_attn_talk": "attention",
     "lumen_attn_talk_prompt": "attention", "lumen_argmax": "sampling", "lumen_sample": "sampling",
     "lumen_gemm_tc_qkv": "qkv product + q/k norm + cache write",
+    "lumen_conv_silu": "state-space: convolution", "lumen_ssm_scan": "state-space: recurrence",
+    "lumen_gated_part_norm": "state-space: gate + norm", "lumen_xielu": "activation",
+    "lumen_moe_route": "experts: route + group", "lumen_moe_route_x": "experts: route + group",
+    "lumen_moe_group": "experts: route + group", "lumen_moe_identity": "experts: identity",
 }
 
 
@@ -65,6 +99,8 @@ def _class_times(run):
         label = CLASSES.get(name)
         if label is None and name == "lumen_gemm_tc":
             label = f"product {int(args[4])}x{int(args[5])}"
+        if label is None and name == "lumen_moe_product":
+            label = "experts: gate/up product" if int(args[14]) else "experts: down product"
         rec.append([label or name, torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)])
         return rec[-1]
     native.instrument(probe)
@@ -144,16 +180,24 @@ def measure(config, batch, steps, warmup, seed=0):
             "prompt_us_by_class": prompt_classes, "decode_us_by_class": decode_classes, "window": window}
 
 
-def run(design, sizes, batch, steps, warmup):
-    if design != "dabevik":
+DESIGNS = {"dabevik": (SIZES, dabevik_config), "rasezen": (RASEZEN_SIZES, rasezen_config)}
+
+
+def sizes_of(design):
+    if design not in DESIGNS:
         raise ValueError(f"no comparison is written for design {design!r}")
+    return DESIGNS[design][0]
+
+
+def run(design, sizes, batch, steps, warmup):
+    table, make = DESIGNS[design] if design in DESIGNS else (sizes_of(design), None)
     import gc
     import torch
     out = {}
     for name in sizes:
-        s = SIZES[name]
+        s = table[name]
         row = {"sizes": s}
-        for label, cfg in (("dabevik", dabevik_config(s)), ("qwen3", qwen3_config(s))):
+        for label, cfg in ((design, make(s)), ("qwen3", qwen3_config(s))):
             row[label] = measure(cfg, batch, steps, warmup)
             gc.collect()
             torch.cuda.empty_cache()
@@ -170,14 +214,21 @@ def steps_main(argv=None) -> int:
     from .engine import Engine, StepEntry
     from .sampling import SamplingConfig
     ap = argparse.ArgumentParser(prog="lumenllm_b200.compare")
-    ap.add_argument("--design", default="dabevik", choices=["dabevik", "qwen3"])
+    ap.add_argument("--design", default="dabevik", choices=["dabevik", "rasezen", "qwen3"])
+    ap.add_argument("--sizes-of", default=None, choices=sorted(DESIGNS),
+                    help="with --design qwen3: whose table of sizes the twin takes (default dabevik)")
     ap.add_argument("--kind", default="decode", choices=["prompt", "decode"])
     ap.add_argument("--size", default="2k", choices=sorted(SIZES))
     ap.add_argument("--layers", type=int, default=2)
     ap.add_argument("--batch", type=int, default=8)
     a = ap.parse_args(argv)
-    s = dict(SIZES[a.size], layers=a.layers)
-    cfg = dabevik_config(s) if a.design == "dabevik" else qwen3_config(s)
+    table, make = DESIGNS[a.design if a.design in DESIGNS else (a.sizes_of or "dabevik")]
+    s = dict(table[a.size])
+    if "pattern" in s:
+        s["pattern"] = s["pattern"][:a.layers]
+    else:
+        s["layers"] = a.layers
+    cfg = make(s) if a.design in DESIGNS else qwen3_config(s)
     eng = Engine.from_random(cfg, seed=0, std=0.02, dtype="bfloat16", max_tokens=a.batch * CONTEXT,
                              max_slots=max(a.batch, 8), context_size=CONTEXT, use_graphs=False)
     g = torch.Generator().manual_seed(1)

@@ -13,30 +13,26 @@
 // depends on its own row and the expert's weights only, never on the batch or on the order in
 // which the entries of an expert were listed.
 #include "common.cuh"
+#include "mma_utils.cuh"
 
 #define MOE_MAX_LANE_VALS 16      // router outputs a lane holds: up to 512 experts
 #define MOE_MAX_EXPERTS 1024
-#define MOE_TM 32                 // entries a row tile
+#define MOE_TM 32                 // entries a row tile (32-bit products)
+#define MOE_TM_MMA 64             // entries a row tile (tensor-core products)
 #define MOE_TN 64                 // output columns a block
 #define MOE_TK 32
 
 // ---------------------------------------------------------------- route
 // A warp a token. logits float32 [N, Et]; corr float32 [Et] or null; idx int32 [N, top];
 // wt float32 [N, top]. Equal choice scores go to the lower index.
-__global__ void __launch_bounds__(128)
-moe_route_kernel(const float* __restrict__ logits, const float* __restrict__ corr, int Et, int top, float scale,
-                 int* __restrict__ idx, float* __restrict__ wt, int N) {
-    pdl_trigger();
-    pdl_wait();
-    const int lane = threadIdx.x & 31;
-    const int t = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
-    if (t >= N) return;
+__device__ __forceinline__ void route_row(const float* __restrict__ lg, const float* __restrict__ corr, int Et,
+                                          int top, float scale, int* __restrict__ idx, float* __restrict__ wt, int lane) {
     float s[MOE_MAX_LANE_VALS], c[MOE_MAX_LANE_VALS];
     float m = -INFINITY;
 #pragma unroll
     for (int r = 0; r < MOE_MAX_LANE_VALS; ++r) {
         const int e = lane + 32 * r;
-        s[r] = e < Et ? logits[(size_t)t * Et + e] : -INFINITY;
+        s[r] = e < Et ? lg[e] : -INFINITY;
         m = fmaxf(m, s[r]);
     }
     m = warp_max(m);
@@ -74,10 +70,66 @@ moe_route_kernel(const float* __restrict__ logits, const float* __restrict__ cor
         for (int r = 0; r < MOE_MAX_LANE_VALS; ++r)
             if (lane + 32 * r == best_e) c[r] = -INFINITY;        // taken
         if (lane == 0) {
-            idx[(size_t)t * top + k] = best_e;
-            wt[(size_t)t * top + k] = best_s * scale;
+            idx[k] = best_e;
+            wt[k] = best_s * scale;
         }
     }
+}
+
+__global__ void __launch_bounds__(128)
+moe_route_kernel(const float* __restrict__ logits, const float* __restrict__ corr, int Et, int top, float scale,
+                 int* __restrict__ idx, float* __restrict__ wt, int N) {
+    pdl_trigger();
+    pdl_wait();
+    const int lane = threadIdx.x & 31;
+    const int t = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    if (t >= N) return;
+    route_row(logits + (size_t)t * Et, corr, Et, top, scale, idx + (size_t)t * top, wt + (size_t)t * top, lane);
+}
+
+// The router's product and the choice in one kernel, a block a token: the token's row goes to
+// shared memory as float32, every warp takes router rows in turn (W float32 [Et, K]; lanes
+// strided over k, then a butterfly, so a logit's sum has one order whatever the batch), and the
+// first warp routes.
+template <typename TA>
+__global__ void __launch_bounds__(256)
+moe_route_x_kernel(const TA* __restrict__ x, const float* __restrict__ W, int K, const float* __restrict__ corr, int Et,
+                   int top, float scale, int* __restrict__ idx, float* __restrict__ wt) {
+    extern __shared__ __align__(16) float rs[];      // K floats, then Et logits
+    pdl_trigger();
+    pdl_wait();
+    const int t = blockIdx.x, lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarp = blockDim.x >> 5;
+    float* lg = rs + K;
+    for (int i = threadIdx.x; i < K; i += blockDim.x) rs[i] = to_f32(x[(size_t)t * K + i]);
+    __syncthreads();
+    for (int e = warp; e < Et; e += nwarp) {
+        const float* we = W + (size_t)e * K;
+        float acc = 0.0f;
+        for (int i = lane; i < K; i += 32) acc = fmaf(rs[i], we[i], acc);
+        acc = warp_sum(acc);
+        if (lane == 0) lg[e] = acc;
+    }
+    __syncthreads();
+    if (warp == 0) route_row(lg, corr, Et, top, scale, idx + (size_t)t * top, wt + (size_t)t * top, lane);
+}
+
+LUMEN_API int lumen_moe_route_x(const void* x, int x_is_bf16, const float* W, int K, const float* corr, int Et, int top,
+                                float scale, int* idx, float* wt, int N, cudaStream_t stream) {
+    if (N <= 0) return 0;
+    if (Et <= 0 || top <= 0 || top > Et || K <= 0) return LUMEN_ERR_BAD_ARGUMENT;
+    const size_t smem = (size_t)(K + Et) * sizeof(float);
+    if (Et > 32 * MOE_MAX_LANE_VALS || smem > 200 * 1024) return LUMEN_ERR_UNSUPPORTED;
+    if (x_is_bf16) {
+        auto k = moe_route_x_kernel<__nv_bfloat16>;
+        if (smem > 48 * 1024) cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        lumen_launch(k, dim3(N), dim3(256), smem, stream, (const __nv_bfloat16*)x, W, K, corr, Et, top, scale, idx, wt);
+    } else {
+        auto k = moe_route_x_kernel<float>;
+        if (smem > 48 * 1024) cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        lumen_launch(k, dim3(N), dim3(256), smem, stream, (const float*)x, W, K, corr, Et, top, scale, idx, wt);
+    }
+    LUMEN_LAUNCH_CHECK();
+    return 0;
 }
 
 LUMEN_API int lumen_moe_route(const float* logits, const float* corr, int Et, int top, float scale, int* idx,
@@ -93,11 +145,11 @@ LUMEN_API int lumen_moe_route(const float* logits, const float* corr, int Et, in
 // ---------------------------------------------------------------- group
 // One block. entries = N * top; sorted int32 [entries] receives the entries (token * top +
 // choice) of expert 0, then of expert 1, ...; entries of identity experts (idx >= E) are left
-// out. tiles int32 [max_tiles, 3] = (expert, first place in sorted, count <= MOE_TM);
+// out. tiles int32 [max_tiles, 3] = (expert, first place in sorted, count <= tile_rows);
 // n_tiles int32 [1].
 __global__ void __launch_bounds__(1024)
-moe_group_kernel(const int* __restrict__ idx, int entries, int E, int* __restrict__ sorted, int* __restrict__ tiles,
-                 int* __restrict__ n_tiles) {
+moe_group_kernel(const int* __restrict__ idx, int entries, int E, int tile_rows, int* __restrict__ sorted,
+                 int* __restrict__ tiles, int* __restrict__ n_tiles) {
     __shared__ int count[MOE_MAX_EXPERTS], start[MOE_MAX_EXPERTS];
     pdl_trigger();
     pdl_wait();
@@ -113,10 +165,10 @@ moe_group_kernel(const int* __restrict__ idx, int entries, int E, int* __restric
         for (int e = 0; e < E; ++e) {
             const int c = count[e];
             start[e] = at;
-            for (int o = 0; o < c; o += MOE_TM) {
+            for (int o = 0; o < c; o += tile_rows) {
                 tiles[3 * nt] = e;
                 tiles[3 * nt + 1] = at + o;
-                tiles[3 * nt + 2] = min(MOE_TM, c - o);
+                tiles[3 * nt + 2] = min(tile_rows, c - o);
                 ++nt;
             }
             at += c;
@@ -131,13 +183,15 @@ moe_group_kernel(const int* __restrict__ idx, int entries, int E, int* __restric
     }
 }
 
-LUMEN_API int lumen_moe_tile_rows() { return MOE_TM; }
+// Entries a row tile: of the tensor-core products (bfloat16 operands) and of the 32-bit ones.
+LUMEN_API int lumen_moe_tile_rows(int tensor_cores) { return tensor_cores ? MOE_TM_MMA : MOE_TM; }
 
-LUMEN_API int lumen_moe_group(const int* idx, int entries, int E, int* sorted, int* tiles, int* n_tiles,
-                              cudaStream_t stream) {
+LUMEN_API int lumen_moe_group(const int* idx, int entries, int E, int tile_rows, int* sorted, int* tiles,
+                              int* n_tiles, cudaStream_t stream) {
     if (entries <= 0) return 0;
     if (E <= 0 || E > MOE_MAX_EXPERTS) return LUMEN_ERR_UNSUPPORTED;
-    lumen_launch(moe_group_kernel, dim3(1), dim3(1024), 0, stream, idx, entries, E, sorted, tiles, n_tiles);
+    if (tile_rows != MOE_TM && tile_rows != MOE_TM_MMA) return LUMEN_ERR_BAD_ARGUMENT;
+    lumen_launch(moe_group_kernel, dim3(1), dim3(1024), 0, stream, idx, entries, E, tile_rows, sorted, tiles, n_tiles);
     LUMEN_LAUNCH_CHECK();
     return 0;
 }
@@ -224,15 +278,145 @@ moe_product_kernel(const TA* __restrict__ A, const TW* __restrict__ W, const int
     }
 }
 
+// The same products for bfloat16 operands on the tensor cores (mma.sync m16n8k16, float32 sums):
+// a tile of MOE_TM_MMA entries x 64 output columns a block of four warps, each warp 16 of the
+// columns (of gate and of up when GATED) for all rows; 64 values of k a step, staged in shared
+// memory in rows of 72 values (ldmatrix then meets no bank twice), the next step's global loads
+// in flight while the tensor cores work on this one. K must be a multiple of 8 and the operands
+// 16-byte aligned (the host sees to it, else the kernel above runs).
+#define MOE_MK 64
+#define MOE_LD 72
+template <bool GATED>
+__global__ void __launch_bounds__(128)
+moe_product_mma_kernel(const __nv_bfloat16* __restrict__ A, const __nv_bfloat16* __restrict__ W,
+                       const int* __restrict__ sorted, const int* __restrict__ tiles, const int* __restrict__ n_tiles,
+                       const float* __restrict__ wt, void* __restrict__ out, int K, int Nout, int top, int n_tokens) {
+    constexpr int NM = GATED ? 2 : 1;
+    __shared__ __align__(16) __nv_bfloat16 As[MOE_TM_MMA * MOE_LD];
+    __shared__ __align__(16) __nv_bfloat16 Ws[NM * MOE_TN * MOE_LD];
+    __shared__ int rows[MOE_TM_MMA];
+    pdl_trigger();
+    pdl_wait();
+    const int tile = blockIdx.x;
+    if (tile >= *n_tiles) return;
+    const int e = tiles[3 * tile], first = tiles[3 * tile + 1], cnt = tiles[3 * tile + 2];
+    const int n0 = blockIdx.y * MOE_TN;
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    if (tid < MOE_TM_MMA) rows[tid] = tid < cnt ? sorted[first + tid] : -1;
+    __syncthreads();
+    const __nv_bfloat16* We = W + (size_t)e * NM * Nout * K;
+    // this thread's pieces of a step: 4 of the activations (64 rows x 8 pieces of 8 values), 4 of
+    // each weight matrix (64 rows x 8 pieces)
+    const __nv_bfloat16* a_src[4];
+    const __nv_bfloat16* w_src[NM][4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const int li = tid + i * 128, r = li >> 3, c = li & 7;
+        const int entry = rows[r];
+        a_src[i] = entry >= 0 ? A + (size_t)(GATED ? entry / top : entry) * K + c * 8 : nullptr;
+#pragma unroll
+        for (int m = 0; m < NM; ++m)
+            w_src[m][i] = n0 + r < Nout ? We + ((size_t)m * Nout + n0 + r) * K + c * 8 : nullptr;
+    }
+    uint4 a_reg[4], w_reg[NM][4];
+    const uint4 zero = make_uint4(0u, 0u, 0u, 0u);
+    auto fetch = [&](int k0) {
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const int c = (tid + i * 128) & 7;
+            const bool in = k0 + c * 8 < K;
+            a_reg[i] = (a_src[i] && in) ? *reinterpret_cast<const uint4*>(a_src[i] + k0) : zero;
+#pragma unroll
+            for (int m = 0; m < NM; ++m)
+                w_reg[m][i] = (w_src[m][i] && in) ? *reinterpret_cast<const uint4*>(w_src[m][i] + k0) : zero;
+        }
+    };
+    float acc[NM][4][2][4];
+#pragma unroll
+    for (int m = 0; m < NM; ++m)
+#pragma unroll
+        for (int mi = 0; mi < 4; ++mi)
+#pragma unroll
+            for (int ni = 0; ni < 2; ++ni)
+#pragma unroll
+                for (int x = 0; x < 4; ++x) acc[m][mi][ni][x] = 0.0f;
+    fetch(0);
+    for (int k0 = 0; k0 < K; k0 += MOE_MK) {
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const int li = tid + i * 128, r = li >> 3, c = li & 7;
+            *reinterpret_cast<uint4*>(As + r * MOE_LD + c * 8) = a_reg[i];
+#pragma unroll
+            for (int m = 0; m < NM; ++m) *reinterpret_cast<uint4*>(Ws + (m * MOE_TN + r) * MOE_LD + c * 8) = w_reg[m][i];
+        }
+        __syncthreads();
+        if (k0 + MOE_MK < K) fetch(k0 + MOE_MK);
+#pragma unroll
+        for (int kk = 0; kk < MOE_MK; kk += 16) {
+            uint32_t b[NM][4];
+#pragma unroll
+            for (int m = 0; m < NM; ++m) {
+                const int r = m * MOE_TN + warp * 16 + (lane & 7) + ((lane >> 4) << 3), c = kk + ((lane >> 3) & 1) * 8;
+                ldsm_x4(b[m], smem_u32(Ws + r * MOE_LD + c));
+            }
+#pragma unroll
+            for (int mi = 0; mi < 4; ++mi) {
+                uint32_t a[4];
+                ldsm_x4(a, smem_u32(As + (mi * 16 + (lane & 15)) * MOE_LD + kk + (lane >> 4) * 8));
+#pragma unroll
+                for (int m = 0; m < NM; ++m) {
+                    mma_bf16(acc[m][mi][0], a, b[m][0], b[m][1]);
+                    mma_bf16(acc[m][mi][1], a, b[m][2], b[m][3]);
+                }
+            }
+        }
+        __syncthreads();
+    }
+#pragma unroll
+    for (int mi = 0; mi < 4; ++mi)
+#pragma unroll
+        for (int hf = 0; hf < 2; ++hf) {
+            const int entry = rows[mi * 16 + (lane >> 2) + hf * 8];
+            if (entry < 0) continue;
+#pragma unroll
+            for (int ni = 0; ni < 2; ++ni)
+#pragma unroll
+                for (int x = 0; x < 2; ++x) {
+                    const int n = n0 + warp * 16 + ni * 8 + 2 * (lane & 3) + x;
+                    if (n >= Nout) continue;
+                    const float v = acc[0][mi][ni][hf * 2 + x];
+                    if (GATED) {
+                        const float u = acc[NM - 1][mi][ni][hf * 2 + x];
+                        ((__nv_bfloat16*)out)[(size_t)entry * Nout + n] = __float2bfloat16_rn(v / (1.0f + expf(-v)) * u);
+                    } else {
+                        ((float*)out)[((size_t)(entry % top) * n_tokens + entry / top) * Nout + n] = wt[entry] * v;
+                    }
+                }
+        }
+}
+
 // gated != 0: A [tokens, K] -> out [entries, Nout] of A's type, W [E, 2 Nout, K];
 // gated == 0: A [entries, K] -> out float32 [top, tokens, Nout], W [E, Nout, K].
 LUMEN_API int lumen_moe_product(const void* A, int a_is_bf16, const void* W, int w_is_bf16, const int* sorted,
                                 const int* tiles, const int* n_tiles, int max_tiles, const float* wt, void* out,
-                                int K, int Nout, int top, int n_tokens, int gated, cudaStream_t stream) {
+                                int K, int Nout, int top, int n_tokens, int gated, int tensor_cores,
+                                cudaStream_t stream) {
     if (max_tiles <= 0 || n_tokens <= 0) return 0;
     if (K <= 0 || Nout <= 0 || top <= 0) return LUMEN_ERR_BAD_ARGUMENT;
     dim3 grid(max_tiles, (Nout + MOE_TN - 1) / MOE_TN);
     if (grid.y > 65535) return LUMEN_ERR_UNSUPPORTED;
+    if (tensor_cores) {
+        // the tiles must have been made MOE_TM_MMA rows tall (lumen_moe_group)
+        if (!a_is_bf16 || !w_is_bf16 || (K & 7) || ((uintptr_t)A & 15) || ((uintptr_t)W & 15)) return LUMEN_ERR_UNSUPPORTED;
+        if (gated)
+            lumen_launch(moe_product_mma_kernel<true>, grid, dim3(128), 0, stream, (const __nv_bfloat16*)A,
+                         (const __nv_bfloat16*)W, sorted, tiles, n_tiles, wt, out, K, Nout, top, n_tokens);
+        else
+            lumen_launch(moe_product_mma_kernel<false>, grid, dim3(128), 0, stream, (const __nv_bfloat16*)A,
+                         (const __nv_bfloat16*)W, sorted, tiles, n_tiles, wt, out, K, Nout, top, n_tokens);
+        LUMEN_LAUNCH_CHECK();
+        return 0;
+    }
 #define MOE_GO(TA, TW, GATED)                                                                                        \
     lumen_launch(moe_product_kernel<TA, TW, GATED>, grid, dim3(256), 0, stream, (const TA*)A, (const TW*)W, sorted, \
                  tiles, n_tiles, wt, out, K, Nout, top, n_tokens)

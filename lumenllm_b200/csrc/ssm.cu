@@ -26,6 +26,7 @@ __device__ __forceinline__ float softplus_f(float x) { return x > 20.0f ? x : lo
 // projection that start at column c0; in[] before the step's first token of the sequence comes
 // from state[slot][taps - 1 + (t' - first)] (rows oldest to newest, zeros for a new sequence).
 // The state is not written here (conv_state_kernel does, after every reader is done).
+#define CONV_RUN 8
 __global__ void __launch_bounds__(256)
 conv_silu_kernel(const float* __restrict__ u, int S, size_t split_stride, int Wu, int c0, int C,
                  const float* __restrict__ w, const float* __restrict__ bias, int taps,
@@ -34,20 +35,44 @@ conv_silu_kernel(const float* __restrict__ u, int S, size_t split_stride, int Wu
     pdl_trigger();
     pdl_wait();
     const int c = blockIdx.x * blockDim.x + threadIdx.x;
-    const int t = blockIdx.y;
-    if (c >= C || t >= N) return;
-    const int b = tok_seq[t];
-    const int first = cu_q[b];
-    const float* st = state + (size_t)seq_slot[b] * slot_stride;
-    float acc = bias ? bias[c] : 0.0f;
-    for (int j = 0; j < taps; ++j) {
-        const int src = t - taps + 1 + j;
-        float x;
-        if (src >= first) x = sum_parts(u + (size_t)src * Wu + c0 + c, S, split_stride);
-        else x = st[(size_t)(taps - 1 + src - first) * C + c];
-        acc = fmaf(w[(size_t)j * C + c], x, acc);
+    const int t0 = blockIdx.y * CONV_RUN;
+    if (c >= C || t0 >= N) return;
+    // a thread walks CONV_RUN rows of its channel; the taps - 1 inputs before a row stay in
+    // registers from row to row and are fetched anew at the run's first row and wherever a
+    // sequence begins
+    float win[SSM_MAX_TAPS], wk[SSM_MAX_TAPS];
+#pragma unroll
+    for (int j = 0; j < SSM_MAX_TAPS; ++j) wk[j] = j < taps ? w[(size_t)j * C + c] : 0.0f;
+    const float bc = bias ? bias[c] : 0.0f;
+    int b_prev = -1;
+    const int t_end = min(t0 + CONV_RUN, N);
+    for (int t = t0; t < t_end; ++t) {
+        const int b = tok_seq[t];
+        if (t == t0 || b != b_prev) {
+            const int first = cu_q[b];
+            const float* st = state + (size_t)seq_slot[b] * slot_stride;
+#pragma unroll
+            for (int j = 0; j < SSM_MAX_TAPS - 1; ++j)
+                if (j < taps - 1) {
+                    const int src = t - (taps - 1) + j;
+                    win[j] = src >= first ? sum_parts(u + (size_t)src * Wu + c0 + c, S, split_stride)
+                                          : st[(size_t)(taps - 1 + src - first) * C + c];
+                }
+            b_prev = b;
+        }
+        const float x = sum_parts(u + (size_t)t * Wu + c0 + c, S, split_stride);
+        float acc = bc;
+#pragma unroll
+        for (int j = 0; j < SSM_MAX_TAPS - 1; ++j)
+            if (j < taps - 1) acc = fmaf(wk[j], win[j], acc);
+#pragma unroll
+        for (int j = 0; j < SSM_MAX_TAPS; ++j)
+            if (j == taps - 1) acc = fmaf(wk[j], x, acc);
+#pragma unroll
+        for (int j = 0; j < SSM_MAX_TAPS - 1; ++j)
+            if (j < taps - 1) win[j] = (j + 1 < taps - 1) ? win[j + 1] : x;
+        out[(size_t)t * C + c] = silu_f(acc);
     }
-    out[(size_t)t * C + c] = silu_f(acc);
 }
 
 // The state moved on to the end of the step: its rows become the last taps - 1 inputs of the
@@ -122,7 +147,7 @@ LUMEN_API int lumen_conv_silu(const float* u, int n_split, long long split_strid
         LUMEN_LAUNCH_CHECK();
         return 0;
     }
-    lumen_launch(conv_silu_kernel, grid, dim3(256), 0, stream, u, n_split, (size_t)split_stride, Wu, c0, C, w, bias, taps,
+    lumen_launch(conv_silu_kernel, dim3((C + 255) / 256, (N + CONV_RUN - 1) / CONV_RUN), dim3(256), 0, stream, u, n_split, (size_t)split_stride, Wu, c0, C, w, bias, taps,
                  (const float*)state, (size_t)slot_stride, tok_seq, cu_q, seq_slot, out, N);
     LUMEN_LAUNCH_CHECK();
     if (taps > 1) {
@@ -139,19 +164,30 @@ LUMEN_API int lumen_conv_silu(const float* u, int n_split, long long split_strid
 // n = j + NS r, r < R, in registers (NS a power of two up to 32, R up to SSM_R): it decays
 // them, adds dt B[n] x[p], and sums S[n, p] C[n] over its n; the NS threads of a channel add
 // their sums by shuffles in a fixed order. Tokens are staged SSM_CHUNK at a time in shared
-// memory (x, B, C of the head's group, and dt and the decay, which the first threads make from
-// the projection's dt column: dt = softplus(sum + dt_bias), a = exp(-exp(A_log) dt)). The order
+// memory (x, B, C of the head's group by asynchronous copies, the next chunk's under way while
+// this one is worked on; and dt and the decay, which the first threads make from the
+// projection's dt column: dt = softplus(sum + dt_bias), a = exp(-exp(A_log) dt)). The order
 // of every sum depends on the sizes alone, so a token's result is the same however the
 // sequence was cut into steps and whatever else is in the batch.
 #define SSM_R 32
 #define SSM_CHUNK 16
 
-__global__ void __launch_bounds__(1024)
+__device__ __forceinline__ void cp_async4(float* dst, const float* src) {
+    asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"((uint32_t)__cvta_generic_to_shared(dst)), "l"(src) : "memory");
+}
+__device__ __forceinline__ void cp_async16(float* dst, const float* src) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"((uint32_t)__cvta_generic_to_shared(dst)), "l"(src) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+__device__ __forceinline__ void cp_async_wait_all() { asm volatile("cp.async.wait_group 0;" ::: "memory"); }
+
+template <int NS>
+__global__ void __launch_bounds__(256, 1)
 ssm_scan_kernel(const float* __restrict__ xbc, int C, int inner, int H, int P, int Nst, int G,
                 const float* __restrict__ u, int S, size_t split_stride, int Wu, int cdt,
                 const float* __restrict__ dt_bias, const float* __restrict__ A_log, const float* __restrict__ Dskip,
                 float* __restrict__ state, size_t slot_stride, const int* __restrict__ cu_q,
-                const int* __restrict__ seq_slot, float* __restrict__ y, int PB, int NS) {
+                const int* __restrict__ seq_slot, float* __restrict__ y, int PB, int vec) {
     extern __shared__ __align__(16) float sm[];
     pdl_trigger();
     pdl_wait();
@@ -161,50 +197,82 @@ ssm_scan_kernel(const float* __restrict__ xbc, int C, int inner, int H, int P, i
     const int tid = threadIdx.x, j = tid % NS, pl = tid / NS, p = p0 + pl;
     const bool live = pl < PB && p < P;
     const int g = h / (H / G);
-    const int R = (Nst + NS - 1) / NS;
-    float* xs = sm;                                  // [CHUNK][PB]
-    float* Bs = xs + SSM_CHUNK * PB;                 // [CHUNK][Nst]
-    float* Cs = Bs + SSM_CHUNK * Nst;                // [CHUNK][Nst]
-    float* dts = Cs + SSM_CHUNK * Nst;               // [CHUNK]
-    float* decs = dts + SSM_CHUNK;                   // [CHUNK]
+    const int R = j < Nst ? (Nst - j + NS - 1) / NS : 0;      // this thread's n = j + NS r < Nst
+    // two buffers of SSM_CHUNK tokens each: [x: CHUNK x PB | B: CHUNK x Nst | C: CHUNK x Nst | dt | decay]
+    const int buf_floats = SSM_CHUNK * (PB + 2 * Nst) + 2 * SSM_CHUNK;
     float* st = state + (size_t)seq_slot[b] * slot_stride + (size_t)h * Nst * P;
     float s[SSM_R];
 #pragma unroll
     for (int r = 0; r < SSM_R; ++r) {
         const int n = j + NS * r;
-        s[r] = (live && r < R && n < Nst) ? st[(size_t)n * P + p] : 0.0f;
+        s[r] = (live && r < R) ? st[(size_t)n * P + p] : 0.0f;
     }
     const float a_h = -expf(A_log[h]), bias_h = dt_bias[h], d_h = Dskip[h];
-    for (int t0 = 0; t0 < qlen; t0 += SSM_CHUNK) {
+    // asks for a chunk's x, B and C rows (asynchronous copies into buffer `which`) and returns
+    // the raw dt of the token this thread will finish (tid < tokens of the chunk)
+    auto request = [&](int t0, int which) -> float {
+        float* xs = sm + which * buf_floats;
+        float* Bs = xs + SSM_CHUNK * PB;
+        float* Cs = Bs + SSM_CHUNK * Nst;
         const int nt = min(SSM_CHUNK, qlen - t0);
-        __syncthreads();
-        for (int i = tid; i < nt * PB; i += blockDim.x) {
-            const int tt = i / PB, pp = i - tt * PB;
-            xs[i] = (p0 + pp < P) ? xbc[(size_t)(first + t0 + tt) * C + h * P + p0 + pp] : 0.0f;
+        if (vec) {
+            const int pv = PB >> 2, nv = Nst >> 2;
+            for (int i = tid; i < nt * pv; i += blockDim.x) {
+                const int tt = i / pv, pp = (i - tt * pv) << 2;
+                if (p0 + pp < P) cp_async16(xs + tt * PB + pp, xbc + (size_t)(first + t0 + tt) * C + h * P + p0 + pp);
+            }
+            for (int i = tid; i < nt * nv; i += blockDim.x) {
+                const int tt = i / nv, n = (i - tt * nv) << 2;
+                const float* row = xbc + (size_t)(first + t0 + tt) * C + inner + g * Nst + n;
+                cp_async16(Bs + tt * Nst + n, row);
+                cp_async16(Cs + tt * Nst + n, row + (size_t)G * Nst);
+            }
+        } else {
+            for (int i = tid; i < nt * PB; i += blockDim.x) {
+                const int tt = i / PB, pp = i - tt * PB;
+                if (p0 + pp < P) cp_async4(xs + i, xbc + (size_t)(first + t0 + tt) * C + h * P + p0 + pp);
+            }
+            for (int i = tid; i < nt * Nst; i += blockDim.x) {
+                const int tt = i / Nst, n = i - tt * Nst;
+                const float* row = xbc + (size_t)(first + t0 + tt) * C + inner + g * Nst + n;
+                cp_async4(Bs + i, row);
+                cp_async4(Cs + i, row + (size_t)G * Nst);
+            }
         }
-        for (int i = tid; i < nt * Nst; i += blockDim.x) {
-            const int tt = i / Nst, n = i - tt * Nst;
-            const float* row = xbc + (size_t)(first + t0 + tt) * C + inner + g * Nst + n;
-            Bs[i] = row[0];
-            Cs[i] = row[(size_t)G * Nst];
-        }
-        if (tid < nt) {
-            const float dt = softplus_f(sum_parts(u + (size_t)(first + t0 + tid) * Wu + cdt + h, S, split_stride) + bias_h);
+        cp_async_commit();
+        return tid < nt ? sum_parts(u + (size_t)(first + t0 + tid) * Wu + cdt + h, S, split_stride) : 0.0f;
+    };
+    auto finish = [&](int t0, int which, float raw) {
+        float* dts = sm + which * buf_floats + SSM_CHUNK * (PB + 2 * Nst);
+        if (tid < min(SSM_CHUNK, qlen - t0)) {
+            const float dt = softplus_f(raw + bias_h);
             dts[tid] = dt;
-            decs[tid] = expf(a_h * dt);
+            dts[SSM_CHUNK + tid] = expf(a_h * dt);
         }
-        __syncthreads();
+    };
+    float raw = request(0, 0);
+    int which = 0;
+    for (int t0 = 0; t0 < qlen; t0 += SSM_CHUNK, which ^= 1) {
+        const int nt = min(SSM_CHUNK, qlen - t0);
+        finish(t0, which, raw);
+        cp_async_wait_all();
+        __syncthreads();                  // this chunk is in place; everyone is done with the other buffer
+        if (t0 + SSM_CHUNK < qlen) raw = request(t0 + SSM_CHUNK, which ^ 1);
+        const float* xs = sm + which * buf_floats;
+        const float* Bs = xs + SSM_CHUNK * PB;
+        const float* Cs = Bs + SSM_CHUNK * Nst;
+        const float* dts = Cs + SSM_CHUNK * Nst;
+        const float* decs = dts + SSM_CHUNK;
         for (int tt = 0; tt < nt; ++tt) {
             const float dec = decs[tt], x = live ? xs[tt * PB + pl] : 0.0f, dx = dts[tt] * x;
-            const float* Bt = Bs + tt * Nst;
-            const float* Ct = Cs + tt * Nst;
+            const float* Bt = Bs + tt * Nst + j;
+            const float* Ct = Cs + tt * Nst + j;
             float acc = 0.0f;
 #pragma unroll
             for (int r = 0; r < SSM_R; ++r) {
-                const int n = j + NS * r;
-                if (r < R && n < Nst) {
-                    s[r] = fmaf(dec, s[r], dx * Bt[n]);
-                    acc = fmaf(s[r], Ct[n], acc);
+                if (r < R) {
+                    s[r] = fmaf(dec, s[r], dx * Bt[NS * r]);
+                    acc = fmaf(s[r], Ct[NS * r], acc);
                 }
             }
             for (int o = NS >> 1; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
@@ -214,7 +282,7 @@ ssm_scan_kernel(const float* __restrict__ xbc, int C, int inner, int H, int P, i
 #pragma unroll
     for (int r = 0; r < SSM_R; ++r) {
         const int n = j + NS * r;
-        if (live && r < R && n < Nst) st[(size_t)n * P + p] = s[r];
+        if (live && r < R) st[(size_t)n * P + p] = s[r];
     }
 }
 
@@ -231,7 +299,7 @@ LUMEN_API int lumen_ssm_scan(const float* xbc, int H, int P, int Nst, int G, con
     if (Nst > 32 * SSM_R || H > 65535) return LUMEN_ERR_UNSUPPORTED;
     int NS = 1;
     while (NS * SSM_R < Nst) NS <<= 1;
-    int PB = P < 1024 / NS ? P : 1024 / NS;
+    int PB = P < 256 / NS ? P : 256 / NS;      // at most 256 threads a block: the state stays in registers
     // more blocks than SMs where a step has few (sequence, head) pairs: a head's channels are
     // independent of one another, so how they are dealt out changes no result
     while ((long long)n_seqs * H * ((P + PB - 1) / PB) < 2 * 148 && PB * NS > 64 && PB % 2 == 0) PB /= 2;
@@ -239,12 +307,24 @@ LUMEN_API int lumen_ssm_scan(const float* xbc, int H, int P, int Nst, int G, con
     if (zb > 65535) return LUMEN_ERR_UNSUPPORTED;
     int threads = ((PB * NS + 31) / 32) * 32;
     const int inner = H * P, C = inner + 2 * G * Nst;
-    const size_t smem = (size_t)(SSM_CHUNK * (PB + 2 * Nst) + 2 * SSM_CHUNK) * sizeof(float);
+    const size_t smem = 2 * (size_t)(SSM_CHUNK * (PB + 2 * Nst) + 2 * SSM_CHUNK) * sizeof(float);
+    // 16-byte copies where every row piece starts on a 16-byte boundary, else 4-byte ones
+    const int vec = (P % 4 == 0 && PB % 4 == 0 && Nst % 4 == 0 && ((uintptr_t)xbc & 15) == 0) ? 1 : 0;
     if (smem > 200 * 1024) return LUMEN_ERR_UNSUPPORTED;
-    if (smem > 48 * 1024) cudaFuncSetAttribute(ssm_scan_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    lumen_launch(ssm_scan_kernel, dim3(n_seqs, H, zb), dim3(threads), smem, stream, xbc, C, inner, H, P, Nst, G, u, n_split,
-                 (size_t)split_stride, Wu, cdt, dt_bias, A_log, Dskip, state, (size_t)slot_stride, cu_q, seq_slot, y, PB,
-                 NS);
+#define SSM_GO(NS_)                                                                                                   \
+    case NS_: {                                                                                                       \
+        auto k = ssm_scan_kernel<NS_>;                                                                                \
+        if (smem > 48 * 1024) cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);        \
+        lumen_launch(k, dim3(n_seqs, H, zb), dim3(threads), smem, stream, xbc, C, inner, H, P, Nst, G, u, n_split,    \
+                     (size_t)split_stride, Wu, cdt, dt_bias, A_log, Dskip, state, (size_t)slot_stride, cu_q,          \
+                     seq_slot, y, PB, vec);                                                                           \
+        break;                                                                                                        \
+    }
+    switch (NS) {
+        SSM_GO(1) SSM_GO(2) SSM_GO(4) SSM_GO(8) SSM_GO(16) SSM_GO(32)
+        default: return LUMEN_ERR_UNSUPPORTED;
+    }
+#undef SSM_GO
     LUMEN_LAUNCH_CHECK();
     return 0;
 }
@@ -252,33 +332,32 @@ LUMEN_API int lumen_ssm_scan(const float* xbc, int H, int P, int Nst, int G, con
 // ---------------------------------------------------------------- gate, then RMS norm in parts
 // v = y * silu(z), z = columns c0 .. c0 + W - 1 of the projection's partial sums; the row is cut
 // into `parts` equal pieces, each divided by its own root mean square (eps inside the root) and
-// multiplied by w. A warp takes a piece at a time.
+// multiplied by w. All threads make the gated values, a warp sums a piece at a time (lanes
+// strided over it, then a butterfly: an order that depends on the piece's length alone).
 template <typename TOut>
 __global__ void __launch_bounds__(1024)
 gated_part_norm_kernel(const float* __restrict__ y, const float* __restrict__ u, int S, size_t split_stride, int Wu,
                        int c0, const float* __restrict__ w, float eps, int W, int parts, TOut* __restrict__ out) {
-    extern __shared__ __align__(16) float vs[];      // W floats
+    extern __shared__ __align__(16) float vs[];      // W floats, then one scale a part
     pdl_trigger();
     pdl_wait();
     const int t = blockIdx.x;
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarp = blockDim.x >> 5;
     const int len = W / parts;
+    float* scale = vs + W;
+    for (int i = threadIdx.x; i < W; i += blockDim.x) {
+        const float z = sum_parts(u + (size_t)t * Wu + c0 + i, S, split_stride);
+        vs[i] = y[(size_t)t * W + i] * silu_f(z);
+    }
+    __syncthreads();
     for (int g = warp; g < parts; g += nwarp) {
         float ss = 0.0f;
-        for (int e = lane; e < len; e += 32) {
-            const int i = g * len + e;
-            const float z = sum_parts(u + (size_t)t * Wu + c0 + i, S, split_stride);
-            const float v = y[(size_t)t * W + i] * silu_f(z);
-            vs[i] = v;
-            ss += v * v;
-        }
+        for (int e = lane; e < len; e += 32) { const float v = vs[g * len + e]; ss += v * v; }
         ss = warp_sum(ss);
-        const float r = 1.0f / sqrtf(ss / (float)len + eps);
-        for (int e = lane; e < len; e += 32) {
-            const int i = g * len + e;
-            out[(size_t)t * W + i] = from_f32<TOut>(vs[i] * r * w[i]);
-        }
+        if (lane == 0) scale[g] = 1.0f / sqrtf(ss / (float)len + eps);
     }
+    __syncthreads();
+    for (int i = threadIdx.x; i < W; i += blockDim.x) out[(size_t)t * W + i] = from_f32<TOut>(vs[i] * scale[i / len] * w[i]);
 }
 
 LUMEN_API int lumen_gated_part_norm(const float* y, const float* u, int n_split, long long split_stride, int Wu,
@@ -286,11 +365,11 @@ LUMEN_API int lumen_gated_part_norm(const float* y, const float* u, int n_split,
                                     int N, cudaStream_t stream) {
     if (N <= 0) return 0;
     if (W <= 0 || parts <= 0 || W % parts || n_split < 1 || c0 < 0 || c0 + W > Wu) return LUMEN_ERR_BAD_ARGUMENT;
-    const size_t smem = (size_t)W * sizeof(float);
+    const size_t smem = (size_t)(W + parts) * sizeof(float);
     if (smem > 200 * 1024) return LUMEN_ERR_UNSUPPORTED;
-    int threads = parts * 32;
+    int threads = N >= 2 * 148 ? 256 : ((W + 31) / 32) * 32;     // few rows: wide blocks, all loads in flight
     if (threads > 1024) threads = 1024;
-    if (threads < 32) threads = 32;
+    if (threads < 64) threads = 64;
     if (out_is_bf16) {
         auto k = gated_part_norm_kernel<__nv_bfloat16>;
         if (smem > 48 * 1024) cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);

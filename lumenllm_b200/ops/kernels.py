@@ -393,14 +393,20 @@ def xielu(z, act, out_dtype):
     return out
 
 
-MOE_TILE_ROWS = None
+_moe_tile_rows = {}
 
 
-def moe_tile_rows() -> int:
-    global MOE_TILE_ROWS
-    if MOE_TILE_ROWS is None:
-        MOE_TILE_ROWS = int(int_fn("moe", "lumen_moe_tile_rows", [])())
-    return MOE_TILE_ROWS
+def moe_tile_rows(tensor_cores: bool) -> int:
+    """Entries a row tile of the grouped products: of the tensor-core kernel, or of the 32-bit one."""
+    if tensor_cores not in _moe_tile_rows:
+        _moe_tile_rows[tensor_cores] = int(int_fn("moe", "lumen_moe_tile_rows", [c_int])(1 if tensor_cores else 0))
+    return _moe_tile_rows[tensor_cores]
+
+
+def moe_takes_tensor_cores(a_dtype, w) -> bool:
+    """bfloat16 activations and weights whose rows are multiples of 16 bytes go to the tensor
+    cores; everything else (a 32-bit run, odd widths) to the 32-bit grouped product."""
+    return (a_dtype == BF16 and w.dtype == BF16 and w.shape[2] % 8 == 0 and w.data_ptr() % 16 == 0)
 
 
 def moe_route(logits, correction, top, scale):
@@ -420,19 +426,41 @@ def moe_route(logits, correction, top, scale):
     return idx, wt
 
 
-def moe_group(idx, n_experts):
+def moe_route_x(x, router, correction, top, scale):
+    """moe_route with the router's product in the same kernel: x [N, K] in the run's type, router
+    float32 [E, K]; the logits are float32 sums over float32(x) * router."""
+    require(router, F32, "moe_route_x.router")
+    N, Kw = x.shape
+    E = router.shape[0]
+    if router.shape[1] != Kw or not x.is_contiguous() or not x.is_cuda:
+        raise KernelError(f"moe_route_x: rows {tuple(x.shape)} do not fit the router {tuple(router.shape)}")
+    if correction is not None:
+        require(correction, F32, "moe_route_x.correction")
+        if correction.numel() != E:
+            raise KernelError(f"moe_route_x: the correction must have {E} values")
+    idx = torch.empty((N, top), dtype=I32, device=x.device)
+    wt = torch.empty((N, top), dtype=F32, device=x.device)
+    f = fn("moe", "lumen_moe_route_x", [P, c_int, P, c_int, P, c_int, c_int, c_float, P, P, c_int, P])
+    check(f(ptr(x), _is_bf16(x), ptr(router), Kw, ptr(correction), E, int(top), float(scale), ptr(idx), ptr(wt), N,
+            stream_ptr()), "moe_route_x")
+    return idx, wt
+
+
+def moe_group(idx, n_experts, tensor_cores=False):
     """The step's (token, choice) entries in order of their expert, and the row tiles the grouped
-    products walk; entries whose index is >= n_experts are left out. Returns (sorted int32
-    [entries], tiles int32 [max_tiles, 3], n_tiles int32 [1], max_tiles)."""
+    products walk (as tall as the kernel that will walk them takes: `tensor_cores`); entries
+    whose index is >= n_experts are left out. Returns (sorted int32 [entries], tiles int32
+    [max_tiles, 3], n_tiles int32 [1], max_tiles, tensor_cores)."""
     require(idx, I32, "moe_group.idx")
     entries = idx.numel()
-    max_tiles = entries // moe_tile_rows() + min(int(n_experts), entries)
+    rows = moe_tile_rows(bool(tensor_cores))
+    max_tiles = entries // rows + min(int(n_experts), entries)
     sorted_ = torch.empty((entries,), dtype=I32, device=idx.device)
     tiles = torch.empty((max(max_tiles, 1), 3), dtype=I32, device=idx.device)
     n_tiles = torch.empty((1,), dtype=I32, device=idx.device)
-    f = fn("moe", "lumen_moe_group", [P, c_int, c_int, P, P, P, P])
-    check(f(ptr(idx), entries, int(n_experts), ptr(sorted_), ptr(tiles), ptr(n_tiles), stream_ptr()), "moe_group")
-    return sorted_, tiles, n_tiles, max_tiles
+    f = fn("moe", "lumen_moe_group", [P, c_int, c_int, c_int, P, P, P, P])
+    check(f(ptr(idx), entries, int(n_experts), rows, ptr(sorted_), ptr(tiles), ptr(n_tiles), stream_ptr()), "moe_group")
+    return sorted_, tiles, n_tiles, max_tiles, bool(tensor_cores)
 
 
 def moe_product(a, w, group, weights, top, n_tokens, gated):
@@ -441,8 +469,10 @@ def moe_product(a, w, group, weights, top, n_tokens, gated):
     gated: a [entries, K], w [E, D, K] -> float32 [top, tokens, D] with every entry's product
     times its weight at [choice][token]; rows of entries that are left out (identity experts)
     are not written."""
-    sorted_, tiles, n_tiles, max_tiles = group
+    sorted_, tiles, n_tiles, max_tiles, tensor_cores = group
     E, rows, K = w.shape
+    if tensor_cores and not (moe_takes_tensor_cores(a.dtype, w) and a.data_ptr() % 16 == 0):
+        raise KernelError("moe_product: tiles made for the tensor cores, operands that they do not take")
     if a.shape[1] != K or not a.is_contiguous() or not w.is_contiguous():
         raise KernelError(f"moe_product: activations {tuple(a.shape)} do not fit weights {tuple(w.shape)}")
     if gated:
@@ -454,9 +484,11 @@ def moe_product(a, w, group, weights, top, n_tokens, gated):
         n_out = rows
         require(weights, F32, "moe_product.weights")
         out = torch.empty((top, n_tokens, n_out), dtype=F32, device=a.device)
-    f = fn("moe", "lumen_moe_product", [P, c_int, P, c_int, P, P, P, c_int, P, P, c_int, c_int, c_int, c_int, c_int, P])
+    f = fn("moe", "lumen_moe_product", [P, c_int, P, c_int, P, P, P, c_int, P, P, c_int, c_int, c_int, c_int, c_int,
+                                        c_int, P])
     check(f(ptr(a), _is_bf16(a), ptr(w), _is_bf16(w), ptr(sorted_), ptr(tiles), ptr(n_tiles), int(max_tiles),
-            ptr(weights), ptr(out), K, n_out, int(top), int(n_tokens), 1 if gated else 0, stream_ptr()), "moe_product")
+            ptr(weights), ptr(out), K, n_out, int(top), int(n_tokens), 1 if gated else 0, 1 if tensor_cores else 0,
+            stream_ptr()), "moe_product")
     return out
 
 

@@ -165,7 +165,7 @@ class RoutedExperts:
         pre = spec.prefix
         dev = runtime.device
         # the router is multiplied in true 32-bit whatever the run's type
-        self.router = Linear(weights[f"{pre}.router"].to(device=dev, dtype=torch.float32), runtime)
+        self.router = weights[f"{pre}.router"].to(device=dev, dtype=torch.float32).contiguous()
         self.correction = weights[f"{pre}.correction"].to(device=dev, dtype=torch.float32).contiguous()
         wdt = torch.float32 if runtime.is_f32 else None
         stack = lambda names: torch.stack([weights[n] if wdt is None else weights[n].to(wdt) for n in names]).contiguous()
@@ -177,8 +177,10 @@ class RoutedExperts:
 
     def forward(self, y, ctx):
         N = y.shape[0]
-        idx, wt = K.moe_route(self.router(y), self.correction, self.top, self.scale)
-        group = K.moe_group(idx, self.E)
+        idx, wt = K.moe_route_x(y, self.router, self.correction, self.top, self.scale)
+        # bfloat16 operands with rows of whole 16 bytes go to the tensor cores, in both products
+        tc = K.moe_takes_tensor_cores(y.dtype, self.w_gate_up) and K.moe_takes_tensor_cores(y.dtype, self.w_down)
+        group = K.moe_group(idx, self.E, tensor_cores=tc)
         z = K.moe_product(y, self.w_gate_up, group, None, self.top, N, gated=True)
         out = K.moe_product(z, self.w_down, group, wt, self.top, N, gated=False)      # [top, N, D]
         if self.ident:
