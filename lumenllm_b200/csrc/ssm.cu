@@ -160,17 +160,18 @@ LUMEN_API int lumen_conv_silu(const float* u, int n_split, long long split_strid
 
 // ---------------------------------------------------------------- the recurrence
 // A block takes one (sequence, head) and PB of the head's P channels, and walks the sequence's
-// tokens of this step in order. Thread (p, j), j < NS, keeps the state values S[n, p] with
-// n = j + NS r, r < R, in registers (NS a power of two up to 32, R up to SSM_R): it decays
-// them, adds dt B[n] x[p], and sums S[n, p] C[n] over its n; the NS threads of a channel add
-// their sums by shuffles in a fixed order. Tokens are staged SSM_CHUNK at a time in shared
-// memory (x, B, C of the head's group by asynchronous copies, the next chunk's under way while
-// this one is worked on; and dt and the decay, which the first threads make from the
-// projection's dt column: dt = softplus(sum + dt_bias), a = exp(-exp(A_log) dt)). The order
-// of every sum depends on the sizes alone, so a token's result is the same however the
-// sequence was cut into steps and whatever else is in the batch.
+// tokens of this step in order. Thread (p, j), j < NS, keeps 32 state values S[n, p] in
+// registers, n = 4 (j + NS q) + c for q < 8, c < 4 (NS a power of two up to 32, so up to 1,024
+// states; places beyond the state's size hold zeros and stay zero): for every token it decays
+// them, adds dt B[n] x[p], and sums S[n, p] C[n] over its n in four running sums; the NS
+// threads of a channel add their sums by shuffles in a fixed order. Tokens are staged a chunk
+// at a time in shared memory (x, B, C of the head's group by asynchronous copies, the next
+// chunk's under way while this one is worked on, B and C rows padded with zeros to 32 NS values
+// and read four values at a time; and dt and the decay, which the first threads make from the
+// projection's dt column: dt = softplus(sum + dt_bias), a = exp(-exp(A_log) dt)). The order of
+// every sum depends on the sizes alone, so a token's result is the same however the sequence
+// was cut into steps and whatever else is in the batch.
 #define SSM_R 32
-#define SSM_CHUNK 16
 
 __device__ __forceinline__ void cp_async4(float* dst, const float* src) {
     asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"((uint32_t)__cvta_generic_to_shared(dst)), "l"(src) : "memory");
@@ -187,8 +188,9 @@ ssm_scan_kernel(const float* __restrict__ xbc, int C, int inner, int H, int P, i
                 const float* __restrict__ u, int S, size_t split_stride, int Wu, int cdt,
                 const float* __restrict__ dt_bias, const float* __restrict__ A_log, const float* __restrict__ Dskip,
                 float* __restrict__ state, size_t slot_stride, const int* __restrict__ cu_q,
-                const int* __restrict__ seq_slot, float* __restrict__ y, int PB, int vec) {
+                const int* __restrict__ seq_slot, float* __restrict__ y, int PB, int vec, int chunk) {
     extern __shared__ __align__(16) float sm[];
+    constexpr int NP = SSM_R * NS;                   // a staged B or C row, zeros from Nst on
     pdl_trigger();
     pdl_wait();
     const int b = blockIdx.x, h = blockIdx.y, p0 = blockIdx.z * PB;
@@ -197,24 +199,28 @@ ssm_scan_kernel(const float* __restrict__ xbc, int C, int inner, int H, int P, i
     const int tid = threadIdx.x, j = tid % NS, pl = tid / NS, p = p0 + pl;
     const bool live = pl < PB && p < P;
     const int g = h / (H / G);
-    const int R = j < Nst ? (Nst - j + NS - 1) / NS : 0;      // this thread's n = j + NS r < Nst
-    // two buffers of SSM_CHUNK tokens each: [x: CHUNK x PB | B: CHUNK x Nst | C: CHUNK x Nst | dt | decay]
-    const int buf_floats = SSM_CHUNK * (PB + 2 * Nst) + 2 * SSM_CHUNK;
+    // two buffers of `chunk` tokens each: [x: chunk x PB | B: chunk x NP | C: chunk x NP | dt | decay]
+    const int buf_floats = chunk * (PB + 2 * NP) + 2 * chunk;
+    for (int which = 0; which < 2; ++which) {        // the rows' padding, written once
+        float* Bs = sm + which * buf_floats + chunk * PB;
+        for (int i = tid; i < 2 * chunk * NP; i += blockDim.x)
+            if (i % NP >= Nst) Bs[i] = 0.0f;
+    }
     float* st = state + (size_t)seq_slot[b] * slot_stride + (size_t)h * Nst * P;
     float s[SSM_R];
 #pragma unroll
     for (int r = 0; r < SSM_R; ++r) {
-        const int n = j + NS * r;
-        s[r] = (live && r < R) ? st[(size_t)n * P + p] : 0.0f;
+        const int n = 4 * (j + NS * (r >> 2)) + (r & 3);
+        s[r] = (live && n < Nst) ? st[(size_t)n * P + p] : 0.0f;
     }
     const float a_h = -expf(A_log[h]), bias_h = dt_bias[h], d_h = Dskip[h];
     // asks for a chunk's x, B and C rows (asynchronous copies into buffer `which`) and returns
     // the raw dt of the token this thread will finish (tid < tokens of the chunk)
     auto request = [&](int t0, int which) -> float {
         float* xs = sm + which * buf_floats;
-        float* Bs = xs + SSM_CHUNK * PB;
-        float* Cs = Bs + SSM_CHUNK * Nst;
-        const int nt = min(SSM_CHUNK, qlen - t0);
+        float* Bs = xs + chunk * PB;
+        float* Cs = Bs + chunk * NP;
+        const int nt = min(chunk, qlen - t0);
         if (vec) {
             const int pv = PB >> 2, nv = Nst >> 2;
             for (int i = tid; i < nt * pv; i += blockDim.x) {
@@ -224,8 +230,8 @@ ssm_scan_kernel(const float* __restrict__ xbc, int C, int inner, int H, int P, i
             for (int i = tid; i < nt * nv; i += blockDim.x) {
                 const int tt = i / nv, n = (i - tt * nv) << 2;
                 const float* row = xbc + (size_t)(first + t0 + tt) * C + inner + g * Nst + n;
-                cp_async16(Bs + tt * Nst + n, row);
-                cp_async16(Cs + tt * Nst + n, row + (size_t)G * Nst);
+                cp_async16(Bs + tt * NP + n, row);
+                cp_async16(Cs + tt * NP + n, row + (size_t)G * Nst);
             }
         } else {
             for (int i = tid; i < nt * PB; i += blockDim.x) {
@@ -235,54 +241,61 @@ ssm_scan_kernel(const float* __restrict__ xbc, int C, int inner, int H, int P, i
             for (int i = tid; i < nt * Nst; i += blockDim.x) {
                 const int tt = i / Nst, n = i - tt * Nst;
                 const float* row = xbc + (size_t)(first + t0 + tt) * C + inner + g * Nst + n;
-                cp_async4(Bs + i, row);
-                cp_async4(Cs + i, row + (size_t)G * Nst);
+                cp_async4(Bs + tt * NP + n, row);
+                cp_async4(Cs + tt * NP + n, row + (size_t)G * Nst);
             }
         }
         cp_async_commit();
         return tid < nt ? sum_parts(u + (size_t)(first + t0 + tid) * Wu + cdt + h, S, split_stride) : 0.0f;
     };
     auto finish = [&](int t0, int which, float raw) {
-        float* dts = sm + which * buf_floats + SSM_CHUNK * (PB + 2 * Nst);
-        if (tid < min(SSM_CHUNK, qlen - t0)) {
+        float* dts = sm + which * buf_floats + chunk * (PB + 2 * NP);
+        if (tid < min(chunk, qlen - t0)) {
             const float dt = softplus_f(raw + bias_h);
             dts[tid] = dt;
-            dts[SSM_CHUNK + tid] = expf(a_h * dt);
+            dts[chunk + tid] = expf(a_h * dt);
         }
     };
     float raw = request(0, 0);
     int which = 0;
-    for (int t0 = 0; t0 < qlen; t0 += SSM_CHUNK, which ^= 1) {
-        const int nt = min(SSM_CHUNK, qlen - t0);
+    for (int t0 = 0; t0 < qlen; t0 += chunk, which ^= 1) {
+        const int nt = min(chunk, qlen - t0);
         finish(t0, which, raw);
         cp_async_wait_all();
         __syncthreads();                  // this chunk is in place; everyone is done with the other buffer
-        if (t0 + SSM_CHUNK < qlen) raw = request(t0 + SSM_CHUNK, which ^ 1);
+        if (t0 + chunk < qlen) raw = request(t0 + chunk, which ^ 1);
         const float* xs = sm + which * buf_floats;
-        const float* Bs = xs + SSM_CHUNK * PB;
-        const float* Cs = Bs + SSM_CHUNK * Nst;
-        const float* dts = Cs + SSM_CHUNK * Nst;
-        const float* decs = dts + SSM_CHUNK;
+        const float* Bs = xs + chunk * PB;
+        const float* Cs = Bs + chunk * NP;
+        const float* dts = Cs + chunk * NP;
+        const float* decs = dts + chunk;
         for (int tt = 0; tt < nt; ++tt) {
             const float dec = decs[tt], x = live ? xs[tt * PB + pl] : 0.0f, dx = dts[tt] * x;
-            const float* Bt = Bs + tt * Nst + j;
-            const float* Ct = Cs + tt * Nst + j;
-            float acc = 0.0f;
+            const float4* B4 = reinterpret_cast<const float4*>(Bs + tt * NP) + j;
+            const float4* C4 = reinterpret_cast<const float4*>(Cs + tt * NP) + j;
+            float a0 = 0.0f, a1 = 0.0f, a2 = 0.0f, a3 = 0.0f;
 #pragma unroll
-            for (int r = 0; r < SSM_R; ++r) {
-                if (r < R) {
-                    s[r] = fmaf(dec, s[r], dx * Bt[NS * r]);
-                    acc = fmaf(s[r], Ct[NS * r], acc);
-                }
+            for (int q = 0; q < SSM_R / 4; ++q) {
+                const float4 bv = B4[NS * q], cv = C4[NS * q];
+                s[4 * q + 0] = fmaf(dec, s[4 * q + 0], dx * bv.x);
+                s[4 * q + 1] = fmaf(dec, s[4 * q + 1], dx * bv.y);
+                s[4 * q + 2] = fmaf(dec, s[4 * q + 2], dx * bv.z);
+                s[4 * q + 3] = fmaf(dec, s[4 * q + 3], dx * bv.w);
+                a0 = fmaf(s[4 * q + 0], cv.x, a0);
+                a1 = fmaf(s[4 * q + 1], cv.y, a1);
+                a2 = fmaf(s[4 * q + 2], cv.z, a2);
+                a3 = fmaf(s[4 * q + 3], cv.w, a3);
             }
+            float acc = (a0 + a1) + (a2 + a3);
+#pragma unroll
             for (int o = NS >> 1; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
             if (live && j == 0) y[(size_t)(first + t0 + tt) * inner + h * P + p] = fmaf(d_h, x, acc);
         }
     }
 #pragma unroll
     for (int r = 0; r < SSM_R; ++r) {
-        const int n = j + NS * r;
-        if (live && r < R) st[(size_t)n * P + p] = s[r];
+        const int n = 4 * (j + NS * (r >> 2)) + (r & 3);
+        if (live && n < Nst) st[(size_t)n * P + p] = s[r];
     }
 }
 
@@ -307,17 +320,18 @@ LUMEN_API int lumen_ssm_scan(const float* xbc, int H, int P, int Nst, int G, con
     if (zb > 65535) return LUMEN_ERR_UNSUPPORTED;
     int threads = ((PB * NS + 31) / 32) * 32;
     const int inner = H * P, C = inner + 2 * G * Nst;
-    const size_t smem = 2 * (size_t)(SSM_CHUNK * (PB + 2 * Nst) + 2 * SSM_CHUNK) * sizeof(float);
+    const int chunk = NS * SSM_R <= 512 ? 16 : 8;             // tokens staged at a time
+    const size_t smem = 2 * (size_t)(chunk * (PB + 2 * NS * SSM_R) + 2 * chunk) * sizeof(float);
+    if (smem > 200 * 1024) return LUMEN_ERR_UNSUPPORTED;
     // 16-byte copies where every row piece starts on a 16-byte boundary, else 4-byte ones
     const int vec = (P % 4 == 0 && PB % 4 == 0 && Nst % 4 == 0 && ((uintptr_t)xbc & 15) == 0) ? 1 : 0;
-    if (smem > 200 * 1024) return LUMEN_ERR_UNSUPPORTED;
 #define SSM_GO(NS_)                                                                                                   \
     case NS_: {                                                                                                       \
         auto k = ssm_scan_kernel<NS_>;                                                                                \
         if (smem > 48 * 1024) cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);        \
         lumen_launch(k, dim3(n_seqs, H, zb), dim3(threads), smem, stream, xbc, C, inner, H, P, Nst, G, u, n_split,    \
                      (size_t)split_stride, Wu, cdt, dt_bias, A_log, Dskip, state, (size_t)slot_stride, cu_q,          \
-                     seq_slot, y, PB, vec);                                                                           \
+                     seq_slot, y, PB, vec, chunk);                                                                    \
         break;                                                                                                        \
     }
     switch (NS) {
