@@ -85,7 +85,7 @@ CLASSES = {
     "lumen_conv_silu": "state-space: convolution", "lumen_ssm_scan": "state-space: recurrence",
     "lumen_gated_part_norm": "state-space: gate + norm", "lumen_xielu": "activation",
     "lumen_moe_route": "experts: route + group", "lumen_moe_route_x": "experts: route + group",
-    "lumen_moe_group": "experts: route + group", "lumen_moe_identity": "experts: identity",
+    "lumen_moe_group": "experts: route + group",
 }
 
 

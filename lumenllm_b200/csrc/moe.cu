@@ -8,7 +8,8 @@
 //   3. two grouped products: gate and up with SiLU(gate) * up behind them, then down with the
 //      entry's weight, written to out[choice][token][:] so that the consumer adds a token's
 //      choices in rising order, like the partial sums of a split product.
-//   4. identity experts (indices from n_experts on): out[choice][token][:] = weight * input.
+//   4. identity experts (indices from n_experts on): out[choice][token][:] = weight * input,
+//      written by the routing kernel, which has the token's row at hand.
 // Every output element is one dot product summed over k in rising order by one thread, so it
 // depends on its own row and the expert's weights only, never on the batch or on the order in
 // which the entries of an expert were listed.
@@ -90,11 +91,12 @@ moe_route_kernel(const float* __restrict__ logits, const float* __restrict__ cor
 // The router's product and the choice in one kernel, a block a token: the token's row goes to
 // shared memory as float32, every warp takes router rows in turn (W float32 [Et, K]; lanes
 // strided over k, then a butterfly, so a logit's sum has one order whatever the batch), and the
-// first warp routes.
+// first warp routes. With ident_out the identity experts' share of the update is written here too.
 template <typename TA>
 __global__ void __launch_bounds__(256)
 moe_route_x_kernel(const TA* __restrict__ x, const float* __restrict__ W, int K, const float* __restrict__ corr, int Et,
-                   int top, float scale, int* __restrict__ idx, float* __restrict__ wt) {
+                   int top, float scale, int* __restrict__ idx, float* __restrict__ wt, float* __restrict__ ident_out,
+                   int E, int n_tokens) {
     extern __shared__ __align__(16) float rs[];      // K floats, then Et logits
     pdl_trigger();
     pdl_wait();
@@ -111,10 +113,20 @@ moe_route_x_kernel(const TA* __restrict__ x, const float* __restrict__ W, int K,
     }
     __syncthreads();
     if (warp == 0) route_row(lg, corr, Et, top, scale, idx + (size_t)t * top, wt + (size_t)t * top, lane);
+    if (!ident_out) return;
+    // choices that fell on identity experts (indices from E on): the token's own row times the
+    // weight, at the choice's place in the update's stack [top, tokens, K]
+    __syncthreads();
+    for (int k = 0; k < top; ++k) {
+        if (idx[(size_t)t * top + k] < E) continue;
+        const float w = wt[(size_t)t * top + k];
+        float* o = ident_out + ((size_t)k * n_tokens + t) * K;
+        for (int i = threadIdx.x; i < K; i += blockDim.x) o[i] = w * rs[i];
+    }
 }
 
 LUMEN_API int lumen_moe_route_x(const void* x, int x_is_bf16, const float* W, int K, const float* corr, int Et, int top,
-                                float scale, int* idx, float* wt, int N, cudaStream_t stream) {
+                                float scale, int* idx, float* wt, float* ident_out, int E, int N, cudaStream_t stream) {
     if (N <= 0) return 0;
     if (Et <= 0 || top <= 0 || top > Et || K <= 0) return LUMEN_ERR_BAD_ARGUMENT;
     const size_t smem = (size_t)(K + Et) * sizeof(float);
@@ -122,11 +134,13 @@ LUMEN_API int lumen_moe_route_x(const void* x, int x_is_bf16, const float* W, in
     if (x_is_bf16) {
         auto k = moe_route_x_kernel<__nv_bfloat16>;
         if (smem > 48 * 1024) cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        lumen_launch(k, dim3(N), dim3(256), smem, stream, (const __nv_bfloat16*)x, W, K, corr, Et, top, scale, idx, wt);
+        lumen_launch(k, dim3(N), dim3(256), smem, stream, (const __nv_bfloat16*)x, W, K, corr, Et, top, scale, idx, wt,
+                     ident_out, E, N);
     } else {
         auto k = moe_route_x_kernel<float>;
         if (smem > 48 * 1024) cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        lumen_launch(k, dim3(N), dim3(256), smem, stream, (const float*)x, W, K, corr, Et, top, scale, idx, wt);
+        lumen_launch(k, dim3(N), dim3(256), smem, stream, (const float*)x, W, K, corr, Et, top, scale, idx, wt, ident_out,
+                     E, N);
     }
     LUMEN_LAUNCH_CHECK();
     return 0;
@@ -425,35 +439,6 @@ LUMEN_API int lumen_moe_product(const void* A, int a_is_bf16, const void* W, int
     else if (!a_is_bf16 && !w_is_bf16) { if (gated) MOE_GO(float, float, true); else MOE_GO(float, float, false); }
     else return LUMEN_ERR_UNSUPPORTED;
 #undef MOE_GO
-    LUMEN_LAUNCH_CHECK();
-    return 0;
-}
-
-// ---------------------------------------------------------------- identity experts
-// out[k][t][:] = wt[t, k] * x[t][:] for the entries whose expert index is >= E.
-template <typename TA>
-__global__ void moe_identity_kernel(const TA* __restrict__ x, const int* __restrict__ idx, const float* __restrict__ wt,
-                                    float* __restrict__ out, int E, int top, int n_tokens, int D) {
-    pdl_trigger();
-    pdl_wait();
-    const int entry = blockIdx.x;
-    if (idx[entry] < E) return;
-    const int t = entry / top, k = entry % top;
-    const float w = wt[entry];
-    float* o = out + ((size_t)k * n_tokens + t) * D;
-    for (int i = threadIdx.x; i < D; i += blockDim.x) o[i] = w * to_f32(x[(size_t)t * D + i]);
-}
-
-LUMEN_API int lumen_moe_identity(const void* x, int x_is_bf16, const int* idx, const float* wt, float* out, int E,
-                                 int top, int n_tokens, int D, cudaStream_t stream) {
-    if (n_tokens <= 0) return 0;
-    if (D <= 0 || top <= 0) return LUMEN_ERR_BAD_ARGUMENT;
-    if (x_is_bf16)
-        lumen_launch(moe_identity_kernel<__nv_bfloat16>, dim3(n_tokens * top), dim3(128), 0, stream,
-                     (const __nv_bfloat16*)x, idx, wt, out, E, top, n_tokens, D);
-    else
-        lumen_launch(moe_identity_kernel<float>, dim3(n_tokens * top), dim3(128), 0, stream, (const float*)x, idx, wt, out,
-                     E, top, n_tokens, D);
     LUMEN_LAUNCH_CHECK();
     return 0;
 }

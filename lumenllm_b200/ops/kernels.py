@@ -426,9 +426,11 @@ def moe_route(logits, correction, top, scale):
     return idx, wt
 
 
-def moe_route_x(x, router, correction, top, scale):
+def moe_route_x(x, router, correction, top, scale, identity_out=None, n_experts=0):
     """moe_route with the router's product in the same kernel: x [N, K] in the run's type, router
-    float32 [E, K]; the logits are float32 sums over float32(x) * router."""
+    float32 [E, K]; the logits are float32 sums over float32(x) * router. With identity_out
+    (float32 [top, N, K]) the choices whose index is >= n_experts are filled in there at once:
+    weight * float32(x[token]) at [choice][token]."""
     require(router, F32, "moe_route_x.router")
     N, Kw = x.shape
     E = router.shape[0]
@@ -438,11 +440,15 @@ def moe_route_x(x, router, correction, top, scale):
         require(correction, F32, "moe_route_x.correction")
         if correction.numel() != E:
             raise KernelError(f"moe_route_x: the correction must have {E} values")
+    if identity_out is not None:
+        require(identity_out, F32, "moe_route_x.identity_out")
+        if tuple(identity_out.shape) != (top, N, Kw):
+            raise KernelError(f"moe_route_x: identity_out {tuple(identity_out.shape)} is not [{top}, {N}, {Kw}]")
     idx = torch.empty((N, top), dtype=I32, device=x.device)
     wt = torch.empty((N, top), dtype=F32, device=x.device)
-    f = fn("moe", "lumen_moe_route_x", [P, c_int, P, c_int, P, c_int, c_int, c_float, P, P, c_int, P])
-    check(f(ptr(x), _is_bf16(x), ptr(router), Kw, ptr(correction), E, int(top), float(scale), ptr(idx), ptr(wt), N,
-            stream_ptr()), "moe_route_x")
+    f = fn("moe", "lumen_moe_route_x", [P, c_int, P, c_int, P, c_int, c_int, c_float, P, P, P, c_int, c_int, P])
+    check(f(ptr(x), _is_bf16(x), ptr(router), Kw, ptr(correction), E, int(top), float(scale), ptr(idx), ptr(wt),
+            ptr(identity_out), int(n_experts), N, stream_ptr()), "moe_route_x")
     return idx, wt
 
 
@@ -463,12 +469,12 @@ def moe_group(idx, n_experts, tensor_cores=False):
     return sorted_, tiles, n_tiles, max_tiles, bool(tensor_cores)
 
 
-def moe_product(a, w, group, weights, top, n_tokens, gated):
+def moe_product(a, w, group, weights, top, n_tokens, gated, out=None):
     """A grouped product over the tiles of moe_group. gated: a [tokens, K] in the run's type, w
     [E, 2 F, K] (gate rows, then up rows) -> silu(gate) * up as [entries, F] in a's type. Not
     gated: a [entries, K], w [E, D, K] -> float32 [top, tokens, D] with every entry's product
-    times its weight at [choice][token]; rows of entries that are left out (identity experts)
-    are not written."""
+    times its weight at [choice][token] (into `out` when given); rows of entries that are left
+    out (identity experts) are not written."""
     sorted_, tiles, n_tiles, max_tiles, tensor_cores = group
     E, rows, K = w.shape
     if tensor_cores and not (moe_takes_tensor_cores(a.dtype, w) and a.data_ptr() % 16 == 0):
@@ -483,28 +489,15 @@ def moe_product(a, w, group, weights, top, n_tokens, gated):
     else:
         n_out = rows
         require(weights, F32, "moe_product.weights")
-        out = torch.empty((top, n_tokens, n_out), dtype=F32, device=a.device)
+        if out is None:
+            out = torch.empty((top, n_tokens, n_out), dtype=F32, device=a.device)
+        elif out.dtype != F32 or tuple(out.shape) != (top, n_tokens, n_out) or not out.is_contiguous():
+            raise KernelError(f"moe_product: out {tuple(out.shape)} is not float32 [{top}, {n_tokens}, {n_out}]")
     f = fn("moe", "lumen_moe_product", [P, c_int, P, c_int, P, P, P, c_int, P, P, c_int, c_int, c_int, c_int, c_int,
                                         c_int, P])
     check(f(ptr(a), _is_bf16(a), ptr(w), _is_bf16(w), ptr(sorted_), ptr(tiles), ptr(n_tiles), int(max_tiles),
             ptr(weights), ptr(out), K, n_out, int(top), int(n_tokens), 1 if gated else 0, 1 if tensor_cores else 0,
             stream_ptr()), "moe_product")
-    return out
-
-
-def moe_identity(x, idx, weights, out, n_experts):
-    """out[choice][token][:] = weight * x[token][:] for the entries whose expert index is >=
-    n_experts (experts that hand their input on). x [N, D]; out float32 [top, N, D]."""
-    require(idx, I32, "moe_identity.idx")
-    require(weights, F32, "moe_identity.weights")
-    require(out, F32, "moe_identity.out")
-    N, D = x.shape
-    top = idx.shape[1]
-    if tuple(out.shape) != (top, N, D) or not x.is_contiguous():
-        raise KernelError(f"moe_identity: out {tuple(out.shape)} does not fit {top} choices of {N} rows of {D}")
-    f = fn("moe", "lumen_moe_identity", [P, c_int, P, P, P, c_int, c_int, c_int, c_int, P])
-    check(f(ptr(x), _is_bf16(x), ptr(idx), ptr(weights), ptr(out), int(n_experts), top, N, D, stream_ptr()),
-          "moe_identity")
     return out
 
 

@@ -201,7 +201,9 @@ class WideNormAttention:
     def state_shape(self):
         return None
 
-    def forward(self, y, ctx, entry):
+    adds_residual = True      # forward takes `residual` and may add its update to it in place
+
+    def forward(self, y, ctx, entry, residual=None):
         kc, vc, table = entry.cache()
         qkv = self.qkv(y, split_ok=True)
         rot = self.position.rotary_dim
@@ -211,4 +213,4 @@ class WideNormAttention:
                                   cs=self.position.angles(ctx) if rot else None, rotary_dim=rot,
                                   value_unit_eps=self.eps if self.value_norm else None)
         out = causal_attention(q, kc, vc, table, ctx, entry.layout, entry.v_layout, self.window, self.scale)
-        return self.o(out.view(-1, self.H * self.dv), split_ok=True)
+        return self.o(out.view(-1, self.H * self.dv), split_ok=True, add_to=residual)

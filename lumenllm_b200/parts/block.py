@@ -135,10 +135,21 @@ class ParallelBlock:
         return all(getattr(p, "graph_safe", False) for p in [self.mixer] + ([self.ffn] if self.ffn else []))
 
     def forward(self, h, pending, ctx, entry):
+        # Both sublayers read y, which is made before either of them touches the stream: a part that
+        # says `adds_residual` is offered the stream and may add its update there in place (a
+        # prompt-sized product does so in its epilogue) and return None.
         y = self.norm.forward(h, pending, self.runtime.dtype)
-        a = self.mixer.forward(y, ctx, entry)
-        if self.ffn is None:
-            return h, a
-        m = self.ffn.forward(y, ctx)
-        stack = lambda d: d if d.dim() == 3 else d.unsqueeze(0)
-        return h, torch.cat([stack(a), stack(m)], dim=0)
+        if getattr(self.mixer, "adds_residual", False):
+            a = self.mixer.forward(y, ctx, entry, residual=h)
+        else:
+            a = self.mixer.forward(y, ctx, entry)
+        m = None
+        if self.ffn is not None:
+            if getattr(self.ffn, "adds_residual", False):
+                m = self.ffn.forward(y, ctx, residual=h)
+            else:
+                m = self.ffn.forward(y, ctx)
+        left = [d if d.dim() == 3 else d.unsqueeze(0) for d in (a, m) if d is not None]
+        if not left:
+            return h, None
+        return h, left[0] if len(left) == 1 else torch.cat(left, dim=0)

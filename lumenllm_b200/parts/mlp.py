@@ -119,9 +119,11 @@ class XieluMLP:
         self.down = Linear(weights[f"{spec.prefix}.down"], runtime)
         self.act = weights[f"{spec.prefix}.act"].to(device=runtime.device, dtype=torch.float32).contiguous()
 
-    def forward(self, y, ctx):
+    adds_residual = True      # forward takes `residual` and may add its update to it in place
+
+    def forward(self, y, ctx, residual=None):
         u = self.up(y, split_ok=True)                       # float32 [N, I], possibly S partials
-        return self.down(K.xielu(u, self.act, self.runtime.dtype), split_ok=True)
+        return self.down(K.xielu(u, self.act, self.runtime.dtype), split_ok=True, add_to=residual)
 
 
 @register_part("ffn", "routed_experts")
@@ -175,17 +177,23 @@ class RoutedExperts:
         self.w_down = stack([f"{pre}.e{e}.down" for e in range(self.E)])    # [E, D, F]
         self.shared = SwiGLU(self._shared_spec(spec), weights, runtime) if Fs else None
 
-    def forward(self, y, ctx):
+    adds_residual = True      # forward takes `residual`; the shared expert may add its update there in place
+
+    def forward(self, y, ctx, residual=None):
         N = y.shape[0]
-        idx, wt = K.moe_route_x(y, self.router, self.correction, self.top, self.scale)
+        # one slice of the update for each of a token's choices; the routing kernel fills in the
+        # identity experts' slices, the down product the others
+        out = torch.empty((self.top, N, self.D), dtype=torch.float32, device=y.device)
+        idx, wt = K.moe_route_x(y, self.router, self.correction, self.top, self.scale,
+                                identity_out=out if self.ident else None, n_experts=self.E)
         # bfloat16 operands with rows of whole 16 bytes go to the tensor cores, in both products
         tc = K.moe_takes_tensor_cores(y.dtype, self.w_gate_up) and K.moe_takes_tensor_cores(y.dtype, self.w_down)
         group = K.moe_group(idx, self.E, tensor_cores=tc)
         z = K.moe_product(y, self.w_gate_up, group, None, self.top, N, gated=True)
-        out = K.moe_product(z, self.w_down, group, wt, self.top, N, gated=False)      # [top, N, D]
-        if self.ident:
-            K.moe_identity(y, idx, wt, out, self.E)
+        K.moe_product(z, self.w_down, group, wt, self.top, N, gated=False, out=out)
         if self.shared is None:
             return out
-        s = self.shared.forward(y, ctx)
+        s = self.shared.forward(y, ctx, residual=residual)
+        if s is None:
+            return out
         return torch.cat([out, s if s.dim() == 3 else s.unsqueeze(0)], dim=0)

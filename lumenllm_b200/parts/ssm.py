@@ -75,7 +75,9 @@ class StateSpaceMixer:
         inputs [taps - 1, C]."""
         return ((self.n_state + self.n_conv,), torch.float32)
 
-    def forward(self, y, ctx, entry):
+    adds_residual = True      # forward takes `residual` and may add its update to it in place
+
+    def forward(self, y, ctx, entry, residual=None):
         store = entry.state()
         S = store[:, :self.n_state].unflatten(1, (self.H, self.N, self.P))
         conv_state = store[:, self.n_state:].unflatten(1, (self.taps - 1, self.C)) if self.taps > 1 else None
@@ -85,4 +87,4 @@ class StateSpaceMixer:
         yh = K.ssm_scan(xbc, self.H, self.P, self.N, self.G, u, self.inner + self.C, self.dt_bias, self.a_log,
                         self.d_skip, S, ctx.cu_q, ctx.seq_slot, ctx.B)
         v = K.gated_part_norm(yh, u, 0, self.norm_w, self.eps, self.parts, self.runtime.dtype)
-        return self.w_out(v, split_ok=True)
+        return self.w_out(v, split_ok=True, add_to=residual)

@@ -372,7 +372,7 @@ def test_residual_stream_after_every_layer(name, dtype, models, plain):
     for i, e in enumerate(eng.model.schedule):
         view = EntryView(ctx, i, i if i in ctx.cache.group_of else None, True)
         h, pending = eng.model.blocks[e.layer].forward(h, pending, ctx, view)
-        x = h + (pending.sum(0) if pending.dim() == 3 else pending)
+        x = h if pending is None else h + (pending.sum(0) if pending.dim() == 3 else pending)
         close(x, streams[i], dtype, f"{name} after layer {i}", stray_rows=0.05)
 
 
@@ -467,6 +467,29 @@ def test_long_decoding_while_windows_pass_and_pages_go(dtype, models, plain):
     eng.free_slot(slot)
     eng.free_slot(other)
     eng.cache.check()
+    eng.check_kernels()
+
+
+def test_a_long_prompt_whose_products_add_into_the_stream(tmp_path):
+    """A prompt long and wide enough for the output products to add their result to the residual
+    stream in their epilogue (no update is handed on then), both sublayers of a block still
+    reading the same normed rows."""
+    from lumenllm_b200.engine import Engine, StepEntry
+    from lumenllm_b200.ops import kernels as K
+    cfg = config(64, 1024, 1e-6, [
+        layer(attention(4, 2, 64, 64, 0.125, size=300, rot=64), dense(512)),
+        layer(state_space(16, 64, 16, 2, 3, 4), moe(128, 4, 1, 2, 1.5, shared=256))])
+    T = 4900
+    assert K.gemm_tc_adds(T, 1024)
+    folder = write_model(cfg, tmp_path / "wide", seed=70)
+    toks = tokens_of(cfg, (T,), seed=71)[0]
+    want = [0, 1, 299, 300, 301, 2047, T - 2, T - 1]
+    _, w = P.load_model(folder)
+    ref = P.forward(cfg, w, toks)[want]
+    eng = Engine.from_folder(folder, dtype="bfloat16", max_tokens=8192)
+    slot = eng.alloc_slot()
+    got = eng.step([StepEntry(slot, toks, want)])
+    close(got, ref, "bfloat16", stray_rows=0.13)
     eng.check_kernels()
 
 
