@@ -618,7 +618,7 @@ qkv_bias_norm_store_kernel(const float* __restrict__ qkv, int S, size_t split_st
                     const int e = i - Wq, g = e / d, ee = e - g * d;
                     T* tile = kc + ((size_t)page * G + g) * LUMEN_PAGE * d;
                     if (V == 1) tile[tile_offset(k_layout, r, ee, d)] = from_f32<T>(x.v[0]);
-                    else stv<V>(tile + (size_t)r * d + ee, x);
+                    else stv<V>(tile + tile_offset(k_layout, r, ee, d), x);
                 }
             } else {
                 const int e = i - Wq - Wk, g = e / dv, ee = e - g * dv;
@@ -628,7 +628,7 @@ qkv_bias_norm_store_kernel(const float* __restrict__ qkv, int S, size_t split_st
                 }
                 T* tile = vc + ((size_t)page * G + g) * LUMEN_PAGE * dv;
                 if (V == 1) tile[tile_offset(v_layout, r, ee, dv)] = from_f32<T>(x.v[0]);
-                else stv<V>(tile + (size_t)r * dv + ee, x);
+                else stv<V>(tile + tile_offset(v_layout, r, ee, dv), x);
             }
         }
         return;
@@ -651,12 +651,12 @@ qkv_bias_norm_store_kernel(const float* __restrict__ qkv, int S, size_t split_st
             }
             T* tile = kc + ((size_t)page * G + g) * LUMEN_PAGE * d;
             if (V == 1) tile[tile_offset(k_layout, r, ee, d)] = from_f32<T>(x.v[0]);
-            else stv<V>(tile + (size_t)r * d + ee, x);           // plain tiles only (the host sees to it)
+            else stv<V>(tile + tile_offset(k_layout, r, ee, d), x);   // four values never straddle a swizzled piece of eight
         } else {
             const int e = i - Wq - Wk, g = e / dv, ee = e - g * dv;
             T* tile = vc + ((size_t)page * G + g) * LUMEN_PAGE * dv;
             if (V == 1) tile[tile_offset(v_layout, r, ee, dv)] = from_f32<T>(x.v[0]);
-            else stv<V>(tile + (size_t)r * dv + ee, x);
+            else stv<V>(tile + tile_offset(v_layout, r, ee, dv), x);
         }
     }
 }
@@ -696,8 +696,7 @@ LUMEN_API int lumen_qkv_bias_norm_store(const float* qkv, int n_split, long long
     const int Wk = G * d, Wv = G * dv, W = Wq + Wk + Wv;
     const size_t smem = (size_t)(W + (v_unit ? G : 0)) * sizeof(float);
     if (smem > 200 * 1024) return LUMEN_ERR_UNSUPPORTED;
-    const bool v4 = (Wq & 3) == 0 && (d & 3) == 0 && (dv & 3) == 0 && k_layout == LUMEN_LAYOUT_LINEAR &&
-                    v_layout == LUMEN_LAYOUT_LINEAR;
+    const bool v4 = (Wq & 3) == 0 && (d & 3) == 0 && (dv & 3) == 0;
     const int threads = row_threads(v4 ? W / 4 : W, N);
     if (is_bf16)
         qkv_store_launch<__nv_bfloat16>(v4, N, threads, smem, stream, qkv, n_split, (size_t)split_stride, bias, qw, kw,

@@ -107,7 +107,21 @@ moe_route_x_kernel(const TA* __restrict__ x, const float* __restrict__ W, int K,
     for (int e = warp; e < Et; e += nwarp) {
         const float* we = W + (size_t)e * K;
         float acc = 0.0f;
-        for (int i = lane; i < K; i += 32) acc = fmaf(rs[i], we[i], acc);
+        if ((K & 3) == 0) {                       // four values a lane a turn, all loads of a row in flight
+            float a1 = 0.0f, a2 = 0.0f, a3 = 0.0f;
+#pragma unroll 4
+            for (int i = lane * 4; i < K; i += 128) {
+                const float4 wv = *reinterpret_cast<const float4*>(we + i);
+                const float4 xv = *reinterpret_cast<const float4*>(rs + i);
+                acc = fmaf(xv.x, wv.x, acc);
+                a1 = fmaf(xv.y, wv.y, a1);
+                a2 = fmaf(xv.z, wv.z, a2);
+                a3 = fmaf(xv.w, wv.w, a3);
+            }
+            acc = (acc + a1) + (a2 + a3);
+        } else {
+            for (int i = lane; i < K; i += 32) acc = fmaf(rs[i], we[i], acc);
+        }
         acc = warp_sum(acc);
         if (lane == 0) lg[e] = acc;
     }
