@@ -534,13 +534,16 @@ qkv_bias_norm_store_kernel(const float* __restrict__ qkv, int S, size_t split_st
                            const int* __restrict__ table, int table_stride, T* __restrict__ q_out,
                            T* __restrict__ kc, T* __restrict__ vc, int Wq, int Wk, int Wv, int G, int d, int dv,
                            int k_layout, int v_layout, const float* __restrict__ cs, int rot, int v_unit, float eps_v) {
-    extern __shared__ __align__(16) float xs[];  // Wq + Wk + Wv floats, then G floats when v_unit
+    extern __shared__ __align__(16) float xs[];  // Wq + Wk + Wv floats, then G floats, then the token's rot (cos, sin) values
     __shared__ float red[32];
     pdl_trigger();
     pdl_wait();
     const int n = blockIdx.x;
     const int W = Wq + Wk + Wv;
     const float* row = qkv + (size_t)n * W;
+    float* vr = xs + W;
+    float* csn = vr + G;                         // the token's angles, read by every head
+    for (int i = threadIdx.x; i < rot; i += blockDim.x) csn[i] = cs[(size_t)n * rot + i];
     float sq = 0.0f, sk = 0.0f;
     for (int i = threadIdx.x * V; i < W; i += blockDim.x * V) {
         Vals<V> x = ldv<V>(row + i);
@@ -568,7 +571,6 @@ qkv_bias_norm_store_kernel(const float* __restrict__ qkv, int S, size_t split_st
     const int pos = cache_pos[n];
     const int page = table[(size_t)tok_seq[n] * table_stride + pos / LUMEN_PAGE];
     const int r = pos % LUMEN_PAGE;
-    float* vr = xs + W;
     if (rot > 0 || v_unit) {
         // the normed queries and keys go back to shared memory, where the rotation finds a value's
         // partner; a warp a value head sums that head's squares
@@ -593,8 +595,7 @@ qkv_bias_norm_store_kernel(const float* __restrict__ qkv, int S, size_t split_st
             }
         }
         __syncthreads();
-        const int half = rot >> 1;
-        const float* csn = cs + (size_t)n * rot;         // rot/2 pairs of (cos, sin)
+        const int half = rot >> 1;                       // csn: rot/2 pairs of (cos, sin)
         for (int i = threadIdx.x * V; i < W; i += blockDim.x * V) {
             Vals<V> x = ldv<V>(xs + i);
             if (i < Wq + Wk) {
@@ -694,7 +695,7 @@ LUMEN_API int lumen_qkv_bias_norm_store(const float* qkv, int n_split, long long
     if ((k_layout == LUMEN_LAYOUT_SW128 && (!is_bf16 || d % 64)) || (v_layout == LUMEN_LAYOUT_SW128 && (!is_bf16 || dv % 64)))
         return LUMEN_ERR_UNSUPPORTED;
     const int Wk = G * d, Wv = G * dv, W = Wq + Wk + Wv;
-    const size_t smem = (size_t)(W + (v_unit ? G : 0)) * sizeof(float);
+    const size_t smem = (size_t)(W + G + rot) * sizeof(float);
     if (smem > 200 * 1024) return LUMEN_ERR_UNSUPPORTED;
     const bool v4 = (Wq & 3) == 0 && (d & 3) == 0 && (dv & 3) == 0;
     const int threads = row_threads(v4 ? W / 4 : W, N);

@@ -27,9 +27,12 @@ __device__ __forceinline__ float softplus_f(float x) { return x > 20.0f ? x : lo
 // from state[slot][taps - 1 + (t' - first)] (rows oldest to newest, zeros for a new sequence).
 // The state is not written here (conv_state_kernel does, after every reader is done).
 #define CONV_RUN 8
+// TAPS > 0: the number of taps is known when the kernel is compiled (the window then stays in
+// registers and the row loop is unrolled); TAPS == 0: any number up to SSM_MAX_TAPS.
+template <int TAPS>
 __global__ void __launch_bounds__(256)
 conv_silu_kernel(const float* __restrict__ u, int S, size_t split_stride, int Wu, int c0, int C,
-                 const float* __restrict__ w, const float* __restrict__ bias, int taps,
+                 const float* __restrict__ w, const float* __restrict__ bias, int taps_any,
                  const float* __restrict__ state, size_t slot_stride, const int* __restrict__ tok_seq,
                  const int* __restrict__ cu_q, const int* __restrict__ seq_slot, float* __restrict__ out, int N) {
     pdl_trigger();
@@ -37,6 +40,7 @@ conv_silu_kernel(const float* __restrict__ u, int S, size_t split_stride, int Wu
     const int c = blockIdx.x * blockDim.x + threadIdx.x;
     const int t0 = blockIdx.y * CONV_RUN;
     if (c >= C || t0 >= N) return;
+    const int taps = TAPS > 0 ? TAPS : taps_any;
     // a thread walks CONV_RUN rows of its channel; the taps - 1 inputs before a row stay in
     // registers from row to row and are fetched anew at the run's first row and wherever a
     // sequence begins
@@ -46,7 +50,9 @@ conv_silu_kernel(const float* __restrict__ u, int S, size_t split_stride, int Wu
     const float bc = bias ? bias[c] : 0.0f;
     int b_prev = -1;
     const int t_end = min(t0 + CONV_RUN, N);
-    for (int t = t0; t < t_end; ++t) {
+#pragma unroll
+    for (int t = t0; t < t0 + CONV_RUN; ++t) {
+        if (t >= t_end) break;
         const int b = tok_seq[t];
         if (t == t0 || b != b_prev) {
             const int first = cu_q[b];
@@ -147,8 +153,17 @@ LUMEN_API int lumen_conv_silu(const float* u, int n_split, long long split_strid
         LUMEN_LAUNCH_CHECK();
         return 0;
     }
-    lumen_launch(conv_silu_kernel, dim3((C + 255) / 256, (N + CONV_RUN - 1) / CONV_RUN), dim3(256), 0, stream, u, n_split, (size_t)split_stride, Wu, c0, C, w, bias, taps,
-                 (const float*)state, (size_t)slot_stride, tok_seq, cu_q, seq_slot, out, N);
+    const dim3 cgrid((C + 255) / 256, (N + CONV_RUN - 1) / CONV_RUN);
+#define CONV_GO(T_)                                                                                                 \
+    lumen_launch(conv_silu_kernel<T_>, cgrid, dim3(256), 0, stream, u, n_split, (size_t)split_stride, Wu, c0, C, w, \
+                 bias, taps, (const float*)state, (size_t)slot_stride, tok_seq, cu_q, seq_slot, out, N)
+    switch (taps) {
+        case 2: CONV_GO(2); break;
+        case 3: CONV_GO(3); break;
+        case 4: CONV_GO(4); break;
+        default: CONV_GO(0); break;
+    }
+#undef CONV_GO
     LUMEN_LAUNCH_CHECK();
     if (taps > 1) {
         lumen_launch(conv_state_kernel, dim3((C + 255) / 256, n_seqs), dim3(256), 0, stream, u, n_split,

@@ -163,7 +163,8 @@ def test_xielu(dtype):
 ATTENTIONS = [attention(4, 2, 16, 24, 0.3, size=9, rot=8), attention(6, 6, 32, 32, 0.11, rot=32, base=1e6),
               attention(3, 1, 32, 16, 0.2, size=1000), attention(2, 2, 64, 64, 0.15, size=33, rot=64),
               attention(5, 5, 24, 8, 0.5, size=1, rot=2), attention(2, 1, 128, 128, 0.1, size=70, rot=32),
-              attention(3, 3, 40, 72, 0.2, size=64, rot=40, base=77.0), attention(34, 1, 20, 10, 0.4, size=50, rot=4)]
+              attention(3, 3, 40, 72, 0.2, size=64, rot=40, base=77.0), attention(34, 1, 20, 10, 0.4, size=50, rot=4),
+              attention(2, 1, 64, 128, 0.12, size=90, rot=16), attention(40, 2, 64, 64, 0.12, size=100, rot=64)]
 
 
 def attention_part(m, D, dtype, seed, edit=None):
@@ -317,7 +318,7 @@ def test_router_choices_and_weights():
 
 
 MIXTURES = [moe(24, 4, 1, 2, 1.5, shared=32), moe(40, 3, 0, 1, 1.0), moe(16, 5, 2, 3, 0.7, shared=8),
-            moe(8, 40, 0, 4, 2.0), moe(72, 2, 3, 5, 1.0, shared=100)]
+            moe(8, 40, 0, 4, 2.0), moe(72, 2, 3, 5, 1.0, shared=100), moe(20, 3, 1, 2, 1.0, shared=12)]
 
 
 @pytest.mark.parametrize("dtype", [F32, BF16])
@@ -354,6 +355,31 @@ def test_whole_prompts(name, dtype, models, plain):
         close(got, plain_logits(plain, name, toks), dtype, f"{name} {len(toks)} tokens", stray_rows=0.03)
     eng.check_kernels()
     eng.cache.check()
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_a_model_without_attention(dtype, tmp_path):
+    """Only state-space layers: no cache group at all, the sequences' state is everything that is
+    kept; a prompt, portions, single tokens, and two requests in a batch."""
+    from lumenllm_b200.engine import Engine, StepEntry
+    cfg = config(50, 48, 1e-5, [layer(state_space(3, 16, 12, 3, 2, 1), dense(40)),
+                                layer(state_space(2, 8, 36, 1, 3, 2), None)])
+    folder = write_model(cfg, tmp_path / "m", seed=80)
+    _, w = P.load_model(folder)
+    a, b = tokens_of(cfg, (150, 40), seed=81)
+    ra, rb = P.forward(cfg, w, a), P.forward(cfg, w, b)
+    eng = Engine.from_folder(folder, dtype=dtype, max_tokens=1024, max_slots=2)
+    assert not eng.cache.groups
+    sa, sb = eng.alloc_slot(), eng.alloc_slot()
+    got = eng.step([StepEntry(sa, a[:100], list(range(100))), StepEntry(sb, b[:7], list(range(7)))])
+    close(got, torch.cat([ra[:100], rb[:7]]), dtype)
+    got = eng.step([StepEntry(sa, a[100:103], [0, 1, 2]), StepEntry(sb, b[7:39], list(range(32)))])
+    close(got, torch.cat([ra[100:103], rb[7:39]]), dtype)
+    rows = [eng.step([StepEntry(sa, [a[t]], [0])] + ([StepEntry(sb, [b[39]], [0])] if t == 103 else []))
+            for t in range(103, 150)]
+    close(torch.cat([r[:1] for r in rows]), ra[103:], dtype)
+    close(rows[0][1:], rb[39:], dtype)
+    eng.check_kernels()
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
