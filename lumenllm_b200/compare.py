@@ -30,11 +30,11 @@ SIZES = {
 RASEZEN_SIZES = {
     "2k": dict(width=2048, heads=16, kv_heads=4, dim=128, ff=8192, window=1024, vocab=32768,
                ssm=dict(heads=64, vdim=64, state=128, groups=8, conv=4, norm_groups=8),
-               moe=dict(ff=1024, experts=16, identity=2, top=4, scale=2.5, shared=2048),
+               moe=dict(ff=1024, experts=16, identity=2, top=4, scale=2.0, shared=2048),
                pattern=["ad", "se", "ae", "ae", "se", "ae", "ad", "se"]),
     "4k": dict(width=4096, heads=32, kv_heads=8, dim=128, ff=12288, window=2048, vocab=32768,
                ssm=dict(heads=128, vdim=64, state=128, groups=8, conv=4, norm_groups=8),
-               moe=dict(ff=1536, experts=16, identity=2, top=4, scale=2.5, shared=3072),
+               moe=dict(ff=1536, experts=16, identity=2, top=4, scale=2.0, shared=3072),
                pattern=["ad", "se", "ae", "se"]),
 }
 CONTEXT = 4096

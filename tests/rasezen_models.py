@@ -65,7 +65,7 @@ SMALL = {
     # pages and of less than one; a state spread over four threads; more identity experts than
     # choices
     "Z": config(211, 128, 3e-6, [
-        layer(attention(4, 2, 64, 64, 0.12, size=150, rot=32), moe(48, 6, 3, 2, 2.5, shared=64)),
+        layer(attention(4, 2, 64, 64, 0.12, size=150, rot=32), moe(48, 6, 3, 2, 2.0, shared=64)),
         layer(state_space(4, 32, 100, 2, 3, 2), dense(96)),
         layer(attention(2, 1, 128, 128, 0.09, size=33, rot=128, base=1e5), dense(160))]),
 }

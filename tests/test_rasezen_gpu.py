@@ -358,6 +358,25 @@ def test_whole_prompts(name, dtype, models, plain):
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
+def test_a_model_whose_rows_are_no_multiples_of_16_bytes(dtype, tmp_path):
+    """Width 44, heads of 6 keys and 10 values, 7 channels a state-space head, experts of 9: no row
+    of any matrix is a multiple of 16 bytes, so the products go the ways that need no alignment."""
+    from lumenllm_b200.engine import Engine, StepEntry
+    cfg = config(61, 44, 1e-5, [layer(attention(3, 1, 6, 10, 0.4, size=20, rot=4), moe(9, 3, 1, 2, 1.2, shared=5)),
+                                layer(state_space(2, 7, 9, 1, 3, 2), dense(30))])
+    folder = write_model(cfg, tmp_path / "m", seed=90)
+    _, w = P.load_model(folder)
+    toks = tokens_of(cfg, (90,), seed=91)[0]
+    ref = P.forward(cfg, w, toks)
+    eng = Engine.from_folder(folder, dtype=dtype, max_tokens=1024, max_slots=2)
+    slot = eng.alloc_slot()
+    got = [eng.step([StepEntry(slot, toks[:70], list(range(70)))])]
+    got += [eng.step([StepEntry(slot, [toks[t]], [0])]) for t in range(70, 90)]
+    close(torch.cat(got), ref, dtype, stray_rows=0.03)
+    eng.check_kernels()
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
 def test_a_model_without_attention(dtype, tmp_path):
     """Only state-space layers: no cache group at all, the sequences' state is everything that is
     kept; a prompt, portions, single tokens, and two requests in a batch."""
