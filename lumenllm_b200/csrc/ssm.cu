@@ -330,7 +330,7 @@ LUMEN_API int lumen_ssm_scan(const float* xbc, int H, int P, int Nst, int G, con
     int PB = P < 256 / NS ? P : 256 / NS;      // at most 256 threads a block: the state stays in registers
     // more blocks than SMs where a step has few (sequence, head) pairs: a head's channels are
     // independent of one another, so how they are dealt out changes no result
-    while ((long long)n_seqs * H * ((P + PB - 1) / PB) < 2 * 148 && PB * NS > 64 && PB % 2 == 0) PB /= 2;
+    while ((long long)n_seqs * H * ((P + PB - 1) / PB) < 2 * 148 && PB * NS > 128 && PB % 2 == 0) PB /= 2;
     const int zb = (P + PB - 1) / PB;
     if (zb > 65535) return LUMEN_ERR_UNSUPPORTED;
     int threads = ((PB * NS + 31) / 32) * 32;
