@@ -19,7 +19,8 @@
 #define MOE_MAX_LANE_VALS 16      // router outputs a lane holds: up to 512 experts
 #define MOE_MAX_EXPERTS 1024
 #define MOE_TM 32                 // entries a row tile (32-bit products)
-#define MOE_TM_MMA 64             // entries a row tile (tensor-core products)
+#define MOE_TM_MMA 64             // entries a row tile (tensor-core products, many entries an expert)
+#define MOE_TM_MMA_FEW 16         // entries a row tile (tensor-core products, few entries an expert)
 #define MOE_TN 64                 // output columns a block
 #define MOE_TK 32
 
@@ -93,7 +94,7 @@ moe_route_kernel(const float* __restrict__ logits, const float* __restrict__ cor
 // strided over k, then a butterfly, so a logit's sum has one order whatever the batch), and the
 // first warp routes. With ident_out the identity experts' share of the update is written here too.
 template <typename TA>
-__global__ void __launch_bounds__(256)
+__global__ void __launch_bounds__(1024)
 moe_route_x_kernel(const TA* __restrict__ x, const float* __restrict__ W, int K, const float* __restrict__ corr, int Et,
                    int top, float scale, int* __restrict__ idx, float* __restrict__ wt, float* __restrict__ ident_out,
                    int E, int n_tokens) {
@@ -109,7 +110,7 @@ moe_route_x_kernel(const TA* __restrict__ x, const float* __restrict__ W, int K,
         float acc = 0.0f;
         if ((K & 3) == 0) {                       // four values a lane a turn, all loads of a row in flight
             float a1 = 0.0f, a2 = 0.0f, a3 = 0.0f;
-#pragma unroll 4
+#pragma unroll 8
             for (int i = lane * 4; i < K; i += 128) {
                 const float4 wv = *reinterpret_cast<const float4*>(we + i);
                 const float4 xv = *reinterpret_cast<const float4*>(rs + i);
@@ -145,15 +146,18 @@ LUMEN_API int lumen_moe_route_x(const void* x, int x_is_bf16, const float* W, in
     if (Et <= 0 || top <= 0 || top > Et || K <= 0) return LUMEN_ERR_BAD_ARGUMENT;
     const size_t smem = (size_t)(K + Et) * sizeof(float);
     if (Et > 32 * MOE_MAX_LANE_VALS || smem > 200 * 1024) return LUMEN_ERR_UNSUPPORTED;
+    // few tokens (decode steps): a warp a router row, all rows at once; many: 8 warps a token
+    int threads = 256;
+    if (N < 2 * 148) threads = Et >= 32 ? 1024 : (Et < 4 ? 128 : 32 * Et);
     if (x_is_bf16) {
         auto k = moe_route_x_kernel<__nv_bfloat16>;
         if (smem > 48 * 1024) cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        lumen_launch(k, dim3(N), dim3(256), smem, stream, (const __nv_bfloat16*)x, W, K, corr, Et, top, scale, idx, wt,
+        lumen_launch(k, dim3(N), dim3(threads), smem, stream, (const __nv_bfloat16*)x, W, K, corr, Et, top, scale, idx, wt,
                      ident_out, E, N);
     } else {
         auto k = moe_route_x_kernel<float>;
         if (smem > 48 * 1024) cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        lumen_launch(k, dim3(N), dim3(256), smem, stream, (const float*)x, W, K, corr, Et, top, scale, idx, wt, ident_out,
+        lumen_launch(k, dim3(N), dim3(threads), smem, stream, (const float*)x, W, K, corr, Et, top, scale, idx, wt, ident_out,
                      E, N);
     }
     LUMEN_LAUNCH_CHECK();
@@ -212,13 +216,16 @@ moe_group_kernel(const int* __restrict__ idx, int entries, int E, int tile_rows,
 }
 
 // Entries a row tile: of the tensor-core products (bfloat16 operands) and of the 32-bit ones.
-LUMEN_API int lumen_moe_tile_rows(int tensor_cores) { return tensor_cores ? MOE_TM_MMA : MOE_TM; }
+// tensor_cores: 0 the 32-bit products, 1 the tensor-core products' tall tiles, 2 their short ones.
+LUMEN_API int lumen_moe_tile_rows(int tensor_cores) {
+    return tensor_cores == 2 ? MOE_TM_MMA_FEW : tensor_cores ? MOE_TM_MMA : MOE_TM;
+}
 
 LUMEN_API int lumen_moe_group(const int* idx, int entries, int E, int tile_rows, int* sorted, int* tiles,
                               int* n_tiles, cudaStream_t stream) {
     if (entries <= 0) return 0;
     if (E <= 0 || E > MOE_MAX_EXPERTS) return LUMEN_ERR_UNSUPPORTED;
-    if (tile_rows != MOE_TM && tile_rows != MOE_TM_MMA) return LUMEN_ERR_BAD_ARGUMENT;
+    if (tile_rows != MOE_TM && tile_rows != MOE_TM_MMA && tile_rows != MOE_TM_MMA_FEW) return LUMEN_ERR_BAD_ARGUMENT;
     lumen_launch(moe_group_kernel, dim3(1), dim3(1024), 0, stream, idx, entries, E, tile_rows, sorted, tiles, n_tiles);
     LUMEN_LAUNCH_CHECK();
     return 0;
@@ -307,22 +314,25 @@ moe_product_kernel(const TA* __restrict__ A, const TW* __restrict__ W, const int
 }
 
 // The same products for bfloat16 operands on the tensor cores (mma.sync m16n8k16, float32 sums):
-// a tile of MOE_TM_MMA entries x 64 output columns a block of four warps, each warp 16 of the
-// columns (of gate and of up when GATED) for all rows; 64 values of k a step, staged in shared
-// memory in rows of 72 values (ldmatrix then meets no bank twice), the next step's global loads
-// in flight while the tensor cores work on this one. K must be a multiple of 8 and the operands
+// a tile of 16 MI entries (MI = 4, or 1 for steps with few entries an expert, whose row tiles
+// would be almost empty and whose time is the tensor cores' work on the empty rows) x 64 output
+// columns a block of four warps, each warp 16 of the columns (of gate and of up when GATED) for
+// all rows; 64 values of k a step, staged in shared
+// memory in rows of 72 values (ldmatrix then meets no bank twice), the next two steps' global
+// loads in flight while the tensor cores work on this one. K must be a multiple of 8 and the operands
 // 16-byte aligned (the host sees to it, else the kernel above runs).
 #define MOE_MK 64
 #define MOE_LD 72
-template <bool GATED>
+template <bool GATED, int MI>
 __global__ void __launch_bounds__(128)
 moe_product_mma_kernel(const __nv_bfloat16* __restrict__ A, const __nv_bfloat16* __restrict__ W,
                        const int* __restrict__ sorted, const int* __restrict__ tiles, const int* __restrict__ n_tiles,
                        const float* __restrict__ wt, void* __restrict__ out, int K, int Nout, int top, int n_tokens) {
     constexpr int NM = GATED ? 2 : 1;
-    __shared__ __align__(16) __nv_bfloat16 As[MOE_TM_MMA * MOE_LD];
+    constexpr int TM = 16 * MI;
+    __shared__ __align__(16) __nv_bfloat16 As[TM * MOE_LD];
     __shared__ __align__(16) __nv_bfloat16 Ws[NM * MOE_TN * MOE_LD];
-    __shared__ int rows[MOE_TM_MMA];
+    __shared__ int rows[TM];
     pdl_trigger();
     pdl_wait();
     const int tile = blockIdx.x;
@@ -330,55 +340,59 @@ moe_product_mma_kernel(const __nv_bfloat16* __restrict__ A, const __nv_bfloat16*
     const int e = tiles[3 * tile], first = tiles[3 * tile + 1], cnt = tiles[3 * tile + 2];
     const int n0 = blockIdx.y * MOE_TN;
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-    if (tid < MOE_TM_MMA) rows[tid] = tid < cnt ? sorted[first + tid] : -1;
+    if (tid < TM) rows[tid] = tid < cnt ? sorted[first + tid] : -1;
     __syncthreads();
     const __nv_bfloat16* We = W + (size_t)e * NM * Nout * K;
-    // this thread's pieces of a step: 4 of the activations (64 rows x 8 pieces of 8 values), 4 of
-    // each weight matrix (64 rows x 8 pieces)
-    const __nv_bfloat16* a_src[4];
+    // this thread's pieces of a step: MI of the activations (16 MI rows x 8 pieces of 8 values), 4
+    // of each weight matrix (64 rows x 8 pieces)
+    const __nv_bfloat16* a_src[MI];
     const __nv_bfloat16* w_src[NM][4];
 #pragma unroll
     for (int i = 0; i < 4; ++i) {
         const int li = tid + i * 128, r = li >> 3, c = li & 7;
-        const int entry = rows[r];
-        a_src[i] = entry >= 0 ? A + (size_t)(GATED ? entry / top : entry) * K + c * 8 : nullptr;
+        if (i < MI) {
+            const int entry = rows[r];
+            a_src[i] = entry >= 0 ? A + (size_t)(GATED ? entry / top : entry) * K + c * 8 : nullptr;
+        }
 #pragma unroll
         for (int m = 0; m < NM; ++m)
             w_src[m][i] = n0 + r < Nout ? We + ((size_t)m * Nout + n0 + r) * K + c * 8 : nullptr;
     }
-    uint4 a_reg[4], w_reg[NM][4];
+    // two k steps of loads are in flight ahead of the tensor cores, in two sets of registers
+    uint4 a_r0[MI], w_r0[NM][4], a_r1[MI], w_r1[NM][4];
     const uint4 zero = make_uint4(0u, 0u, 0u, 0u);
-    auto fetch = [&](int k0) {
+    auto fetch = [&](int k0, uint4 (&a_reg)[MI], uint4 (&w_reg)[NM][4]) {
 #pragma unroll
         for (int i = 0; i < 4; ++i) {
             const int c = (tid + i * 128) & 7;
             const bool in = k0 + c * 8 < K;
-            a_reg[i] = (a_src[i] && in) ? *reinterpret_cast<const uint4*>(a_src[i] + k0) : zero;
+            if (i < MI) a_reg[i] = (a_src[i] && in) ? *reinterpret_cast<const uint4*>(a_src[i] + k0) : zero;
 #pragma unroll
             for (int m = 0; m < NM; ++m)
                 w_reg[m][i] = (w_src[m][i] && in) ? *reinterpret_cast<const uint4*>(w_src[m][i] + k0) : zero;
         }
     };
-    float acc[NM][4][2][4];
+    float acc[NM][MI][2][4];
 #pragma unroll
     for (int m = 0; m < NM; ++m)
 #pragma unroll
-        for (int mi = 0; mi < 4; ++mi)
+        for (int mi = 0; mi < MI; ++mi)
 #pragma unroll
             for (int ni = 0; ni < 2; ++ni)
 #pragma unroll
                 for (int x = 0; x < 4; ++x) acc[m][mi][ni][x] = 0.0f;
-    fetch(0);
-    for (int k0 = 0; k0 < K; k0 += MOE_MK) {
+    // one k step: the registers' pieces go to shared memory, the registers are asked for the step
+    // after the next, the tensor cores work on this one
+    auto step = [&](int k0, uint4 (&a_reg)[MI], uint4 (&w_reg)[NM][4]) {
 #pragma unroll
         for (int i = 0; i < 4; ++i) {
             const int li = tid + i * 128, r = li >> 3, c = li & 7;
-            *reinterpret_cast<uint4*>(As + r * MOE_LD + c * 8) = a_reg[i];
+            if (i < MI) *reinterpret_cast<uint4*>(As + r * MOE_LD + c * 8) = a_reg[i];
 #pragma unroll
             for (int m = 0; m < NM; ++m) *reinterpret_cast<uint4*>(Ws + (m * MOE_TN + r) * MOE_LD + c * 8) = w_reg[m][i];
         }
         __syncthreads();
-        if (k0 + MOE_MK < K) fetch(k0 + MOE_MK);
+        if (k0 + 2 * MOE_MK < K) fetch(k0 + 2 * MOE_MK, a_reg, w_reg);
 #pragma unroll
         for (int kk = 0; kk < MOE_MK; kk += 16) {
             uint32_t b[NM][4];
@@ -388,7 +402,7 @@ moe_product_mma_kernel(const __nv_bfloat16* __restrict__ A, const __nv_bfloat16*
                 ldsm_x4(b[m], smem_u32(Ws + r * MOE_LD + c));
             }
 #pragma unroll
-            for (int mi = 0; mi < 4; ++mi) {
+            for (int mi = 0; mi < MI; ++mi) {
                 uint32_t a[4];
                 ldsm_x4(a, smem_u32(As + (mi * 16 + (lane & 15)) * MOE_LD + kk + (lane >> 4) * 8));
 #pragma unroll
@@ -399,9 +413,15 @@ moe_product_mma_kernel(const __nv_bfloat16* __restrict__ A, const __nv_bfloat16*
             }
         }
         __syncthreads();
+    };
+    fetch(0, a_r0, w_r0);
+    if (MOE_MK < K) fetch(MOE_MK, a_r1, w_r1);
+    for (int k0 = 0; k0 < K; k0 += 2 * MOE_MK) {
+        step(k0, a_r0, w_r0);
+        if (k0 + MOE_MK < K) step(k0 + MOE_MK, a_r1, w_r1);
     }
 #pragma unroll
-    for (int mi = 0; mi < 4; ++mi)
+    for (int mi = 0; mi < MI; ++mi)
 #pragma unroll
         for (int hf = 0; hf < 2; ++hf) {
             const int entry = rows[mi * 16 + (lane >> 2) + hf * 8];
@@ -434,14 +454,14 @@ LUMEN_API int lumen_moe_product(const void* A, int a_is_bf16, const void* W, int
     dim3 grid(max_tiles, (Nout + MOE_TN - 1) / MOE_TN);
     if (grid.y > 65535) return LUMEN_ERR_UNSUPPORTED;
     if (tensor_cores) {
-        // the tiles must have been made MOE_TM_MMA rows tall (lumen_moe_group)
+        // the tiles must have been made as tall as this says (lumen_moe_group): 1 tall, 2 short
         if (!a_is_bf16 || !w_is_bf16 || (K & 7) || ((uintptr_t)A & 15) || ((uintptr_t)W & 15)) return LUMEN_ERR_UNSUPPORTED;
-        if (gated)
-            lumen_launch(moe_product_mma_kernel<true>, grid, dim3(128), 0, stream, (const __nv_bfloat16*)A,
-                         (const __nv_bfloat16*)W, sorted, tiles, n_tiles, wt, out, K, Nout, top, n_tokens);
-        else
-            lumen_launch(moe_product_mma_kernel<false>, grid, dim3(128), 0, stream, (const __nv_bfloat16*)A,
-                         (const __nv_bfloat16*)W, sorted, tiles, n_tiles, wt, out, K, Nout, top, n_tokens);
+#define MOE_MMA_GO(G_, MI_)                                                                                     \
+    lumen_launch(moe_product_mma_kernel<G_, MI_>, grid, dim3(128), 0, stream, (const __nv_bfloat16*)A,          \
+                 (const __nv_bfloat16*)W, sorted, tiles, n_tiles, wt, out, K, Nout, top, n_tokens)
+        if (tensor_cores == 2) { if (gated) MOE_MMA_GO(true, 1); else MOE_MMA_GO(false, 1); }
+        else { if (gated) MOE_MMA_GO(true, 4); else MOE_MMA_GO(false, 4); }
+#undef MOE_MMA_GO
         LUMEN_LAUNCH_CHECK();
         return 0;
     }

@@ -396,10 +396,12 @@ def xielu(z, act, out_dtype):
 _moe_tile_rows = {}
 
 
-def moe_tile_rows(tensor_cores: bool) -> int:
-    """Entries a row tile of the grouped products: of the tensor-core kernel, or of the 32-bit one."""
+def moe_tile_rows(tensor_cores: int) -> int:
+    """Entries a row tile of the grouped products: 0 the 32-bit kernel's, 1 the tensor-core
+    kernel's tall tiles, 2 its short ones (steps with few entries an expert)."""
+    tensor_cores = int(tensor_cores)
     if tensor_cores not in _moe_tile_rows:
-        _moe_tile_rows[tensor_cores] = int(int_fn("moe", "lumen_moe_tile_rows", [c_int])(1 if tensor_cores else 0))
+        _moe_tile_rows[tensor_cores] = int(int_fn("moe", "lumen_moe_tile_rows", [c_int])(tensor_cores))
     return _moe_tile_rows[tensor_cores]
 
 
@@ -456,17 +458,20 @@ def moe_group(idx, n_experts, tensor_cores=False):
     """The step's (token, choice) entries in order of their expert, and the row tiles the grouped
     products walk (as tall as the kernel that will walk them takes: `tensor_cores`); entries
     whose index is >= n_experts are left out. Returns (sorted int32 [entries], tiles int32
-    [max_tiles, 3], n_tiles int32 [1], max_tiles, tensor_cores)."""
+    [max_tiles, 3], n_tiles int32 [1], max_tiles, which tiles: 0, 1 tall or 2 short)."""
     require(idx, I32, "moe_group.idx")
     entries = idx.numel()
-    rows = moe_tile_rows(bool(tensor_cores))
+    # few entries an expert (decode steps): short tiles, else the tensor cores spend the step on
+    # empty rows. A row's sums do not depend on its tile's height, so both give the same bits.
+    tensor_cores = (2 if entries <= 32 * int(n_experts) else 1) if tensor_cores else 0
+    rows = moe_tile_rows(tensor_cores)
     max_tiles = entries // rows + min(int(n_experts), entries)
     sorted_ = torch.empty((entries,), dtype=I32, device=idx.device)
     tiles = torch.empty((max(max_tiles, 1), 3), dtype=I32, device=idx.device)
     n_tiles = torch.empty((1,), dtype=I32, device=idx.device)
     f = fn("moe", "lumen_moe_group", [P, c_int, c_int, c_int, P, P, P, P])
     check(f(ptr(idx), entries, int(n_experts), rows, ptr(sorted_), ptr(tiles), ptr(n_tiles), stream_ptr()), "moe_group")
-    return sorted_, tiles, n_tiles, max_tiles, bool(tensor_cores)
+    return sorted_, tiles, n_tiles, max_tiles, tensor_cores
 
 
 def moe_product(a, w, group, weights, top, n_tokens, gated, out=None):
@@ -496,7 +501,7 @@ def moe_product(a, w, group, weights, top, n_tokens, gated, out=None):
     f = fn("moe", "lumen_moe_product", [P, c_int, P, c_int, P, P, P, c_int, P, P, c_int, c_int, c_int, c_int, c_int,
                                         c_int, P])
     check(f(ptr(a), _is_bf16(a), ptr(w), _is_bf16(w), ptr(sorted_), ptr(tiles), ptr(n_tiles), int(max_tiles),
-            ptr(weights), ptr(out), K, n_out, int(top), int(n_tokens), 1 if gated else 0, 1 if tensor_cores else 0,
+            ptr(weights), ptr(out), K, n_out, int(top), int(n_tokens), 1 if gated else 0, int(tensor_cores),
             stream_ptr()), "moe_product")
     return out
 
