@@ -169,8 +169,8 @@ class RoutedExperts:
         # the router is multiplied in true 32-bit whatever the run's type
         self.router = weights[f"{pre}.router"].to(device=dev, dtype=torch.float32).contiguous()
         self.correction = weights[f"{pre}.correction"].to(device=dev, dtype=torch.float32).contiguous()
-        wdt = torch.float32 if runtime.is_f32 else None
-        stack = lambda names: torch.stack([weights[n] if wdt is None else weights[n].to(wdt) for n in names]).contiguous()
+        # the grouped products take the experts' weights in the run's type
+        stack = lambda names: torch.stack([weights[n].to(runtime.dtype) for n in names]).contiguous()
         gate = stack([f"{pre}.e{e}.gate" for e in range(self.E)])
         up = stack([f"{pre}.e{e}.up" for e in range(self.E)])
         self.w_gate_up = torch.cat([gate, up], dim=1).contiguous()          # [E, 2 F, D]: gate rows, then up rows
